@@ -43,6 +43,9 @@ class PagedGroup:
     entries: list[int]                 # schedule entries that write into this group, in layer order
     allocator: BlockAllocator
     pool: torch.Tensor | None = None   # [layers, 2, pages + 1, kv_heads, page_tokens, head_dim]
+    # where values have another size than keys the two cannot share a tensor: one pool each, `pool` stays None
+    k_store: torch.Tensor | None = None  # [layers, pages + 1, kv_heads, page_tokens, head_dim]
+    v_store: torch.Tensor | None = None  # [layers, pages + 1, kv_heads, page_tokens, v_head_dim]
 
     @property
     def scratch_page(self) -> int:
@@ -64,8 +67,9 @@ class CacheView:
     layer: int                         # index inside the group's pool
     writes: bool = True                # False when the entry reads another entry's keys and values
     k_pool: torch.Tensor | None = None # [pages + 1, kv_heads, page_tokens, head_dim]
-    v_pool: torch.Tensor | None = None
+    v_pool: torch.Tensor | None = None # [pages + 1, kv_heads, page_tokens, head_dim or the values' own size]
     pool: torch.Tensor | None = None   # the group's whole pool [layers, 2, pages + 1, kv_heads, page_tokens, head_dim]
+                                       # (None where values have another size than keys)
     state: torch.Tensor | None = None  # [slots + 1, *shape]
     page_tokens: int = 0
     need: object = None
@@ -142,9 +146,12 @@ class CacheManager:
     def _allocate_pools(self) -> None:
         for group in self.paged:
             need = group.need
-            group.pool = torch.zeros(
-                (len(group.entries), 2, group.allocator.num_blocks + 1, need.kv_heads, self.block_tokens, need.head_dim),
-                dtype=self.dtype, device=self.device)
+            shape = (group.allocator.num_blocks + 1, need.kv_heads, self.block_tokens)
+            if need.value_dim == need.head_dim:
+                group.pool = torch.zeros((len(group.entries), 2, *shape, need.head_dim), dtype=self.dtype, device=self.device)
+            else:
+                group.k_store = torch.zeros((len(group.entries), *shape, need.head_dim), dtype=self.dtype, device=self.device)
+                group.v_store = torch.zeros((len(group.entries), *shape, need.value_dim), dtype=self.dtype, device=self.device)
         for group in self.states:
             group.pool = torch.zeros((len(group.entries), self.max_requests + 1, *group.need.shape),
                                      dtype=group.need.dtype, device=self.device)
@@ -154,8 +161,11 @@ class CacheManager:
                                                pin_memory=True)
         for view in self.views.values():
             if view.kind == "paged":
-                pool = self.paged[view.group].pool
-                view.k_pool, view.v_pool, view.pool = pool[view.layer, 0], pool[view.layer, 1], pool
+                group = self.paged[view.group]
+                if group.pool is not None:
+                    view.k_pool, view.v_pool, view.pool = group.pool[view.layer, 0], group.pool[view.layer, 1], group.pool
+                else:
+                    view.k_pool, view.v_pool = group.k_store[view.layer], group.v_store[view.layer]
             else:
                 view.state = self.states[view.group].pool[view.layer]
 
@@ -171,7 +181,7 @@ class CacheManager:
         return self._slots.num_free
 
     def pool_bytes(self) -> int:
-        pools = [g.pool for g in self.paged] + [g.pool for g in self.states] + [self.records]
+        pools = [t for g in self.paged for t in (g.pool, g.k_store, g.v_store)] + [g.pool for g in self.states] + [self.records]
         return sum(p.numel() * p.element_size() for p in pools if p is not None)
 
     # ------------------------------------------------------------------ arithmetic

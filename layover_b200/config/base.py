@@ -4,6 +4,7 @@ A configuration class reads its own `config.json` keys (`from_hf_dict`) and writ
 (`to_hf_dict`). The registry maps the name found in `config.json` (`architectures[0]`, else
 `model_type`) to an `Architecture`: the configuration class and a function that turns a
 configuration into a `ModelSpec` (the list of layers, their parts and the order they run in).
+A config.json that names its model with a single `architecture` string is read the same way.
 The reference has one hard-wired `model_type` check (layover/config.py:36-37); here a new
 architecture is one `register_architecture` call.
 """
@@ -50,7 +51,7 @@ def supported_architectures() -> list[str]:
 
 def resolve_architecture(raw: dict) -> Architecture:
     """The architecture that a config.json names, or a ValueError listing what is supported."""
-    names = raw.get("architectures") or []
+    names = raw.get("architectures") or ([raw["architecture"]] if isinstance(raw.get("architecture"), str) else [])
     for name in names:
         if name in _BY_NAME:
             return _BY_NAME[name]

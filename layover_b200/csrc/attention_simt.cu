@@ -1,10 +1,14 @@
 // Paged grouped-query attention over the block table, 32-bit arithmetic throughout, one kernel
 // for every segment length: a whole prompt, a portion of one, or a single decoded token.
 //
-//   s_j = (q . K_j) / sqrt(dim)      for keys j <= p and (window == 0 or p - j < window)
+//   s_j = (q . K_j) * scale          for keys j <= p and (window == 0 or p - j < window)
 //   o   = sum_j softmax(s)_j V_j     (layover/model.py:59,90-96; layover/kernels/triton_decode.py:89-119)
 //
-// where p is the query's absolute position. Keys are walked in tiles of 32 aligned to absolute
+// where p is the query's absolute position. Three optional generalisations, each off with a null
+// pointer or an equal size: values of another size than keys (`vdim`, out is [T, q_heads * vdim]);
+// a learned sink per query head, a score without key or value that only enlarges the softmax's
+// denominator, o = sum_j exp(s_j) V_j / (exp(sink_h) + sum_j exp(s_j)); and a gate per (token,
+// head), a 32-bit factor on the head's output. Keys are walked in tiles of 32 aligned to absolute
 // positions (tile i holds keys [32 i, 32 i + 32)), each score is one sequential dot product and
 // the running maximum / sum follow the same recurrence for every row, so a row's result does
 // not depend on how the tokens were cut into steps or on which other rows share its block.
@@ -46,13 +50,14 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
                             T* __restrict__ out, const int* __restrict__ block_table, int table_width,
                             const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                             const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int q_heads,
-                            int kv_heads, int dim, int page_tokens, float scale, int window) {
+                            int kv_heads, int dim, int page_tokens, float scale, int window, int vdim,
+                            const float* __restrict__ sinks, const float* __restrict__ gates) {
   extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
   float* q_s = smem;                               // [BQ][dim]
   float* k_s = q_s + BQ * dim;                     // [BKEYS][dim + 1]
-  float* v_s = k_s + BKEYS * (dim + 1);            // [BKEYS][dim]
+  float* v_s = k_s + BKEYS * (dim + 1);            // [BKEYS][vdim]
 
   const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x];
   const int head = blockIdx.y, kv_head = head / (q_heads / kv_heads);
@@ -86,16 +91,24 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
     for (int i = threadIdx.x; i < BKEYS * quads; i += blockDim.x) {
       const int j = i / quads, c = (i - j * quads) << 2;
       const int key = tile * BKEYS + j;
-      float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+      float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
       if (key >= key_lo && key <= p_last) {
         const size_t page = (size_t)table[key / page_tokens];
-        const size_t at = ((page * kv_heads + kv_head) * page_tokens + key % page_tokens) * dim + c;
-        kv = Quad<T>::load(k_pool + at);
-        vv = Quad<T>::load(v_pool + at);
+        kv = Quad<T>::load(k_pool + ((page * kv_heads + kv_head) * page_tokens + key % page_tokens) * dim + c);
       }
       float* kd = k_s + j * (dim + 1) + c;
       kd[0] = kv.x; kd[1] = kv.y; kd[2] = kv.z; kd[3] = kv.w;
-      *reinterpret_cast<float4*>(v_s + j * dim + c) = vv;
+    }
+    const int vquads = vdim >> 2;
+    for (int i = threadIdx.x; i < BKEYS * vquads; i += blockDim.x) {
+      const int j = i / vquads, c = (i - j * vquads) << 2;
+      const int key = tile * BKEYS + j;
+      float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (key >= key_lo && key <= p_last) {
+        const size_t page = (size_t)table[key / page_tokens];
+        vv = Quad<T>::load(v_pool + ((page * kv_heads + kv_head) * page_tokens + key % page_tokens) * vdim + c);
+      }
+      *reinterpret_cast<float4*>(v_s + j * vdim + c) = vv;
     }
     __syncthreads();
     const int key = tile * BKEYS + lane;
@@ -124,7 +137,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
 #pragma unroll
         for (int c = 0; c < ACC_PER_LANE; ++c) {
           const int d = lane + 32 * c;
-          if (d < dim) acc[r][c] = fmaf(pj, v_s[j * dim + d], acc[r][c]);
+          if (d < vdim) acc[r][c] = fmaf(pj, v_s[j * vdim + d], acc[r][c]);
         }
       }
     }
@@ -133,11 +146,22 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
   for (int r = 0; r < ROWS_PER_WARP; ++r) {
     const int row = warp * ROWS_PER_WARP + r;
     if (row >= n_q) continue;
-    T* o = out + ((size_t)(row0 + q0 + row) * q_heads + head) * dim;
+    T* o = out + ((size_t)(row0 + q0 + row) * q_heads + head) * vdim;
+    float denominator = l[r], keep = 1.f;
+    if (sinks) {                                   // the sink joins the denominator only; m is finite (a row sees itself)
+      const float sink = sinks[head], top = fmaxf(m[r], sink);
+      keep = expf(m[r] - top);
+      denominator = l[r] * keep + expf(sink - top);
+    }
+    const float gate = gates ? gates[(size_t)(row0 + q0 + row) * q_heads + head] : 1.f;
 #pragma unroll
     for (int c = 0; c < ACC_PER_LANE; ++c) {
       const int d = lane + 32 * c;
-      if (d < dim) Elem<T>::store(o + d, acc[r][c] / l[r]);
+      if (d < vdim) {
+        float value = sinks ? acc[r][c] * keep / denominator : acc[r][c] / l[r];
+        if (gates) value *= gate;
+        Elem<T>::store(o + d, value);
+      }
     }
   }
 }
@@ -148,23 +172,26 @@ LB_EXPORT int lb_attention_simt_block_queries() { return BQ; }
 LB_EXPORT int lb_attention_simt(int dtype, const void* q, const void* k_pool, const void* v_pool, void* out,
                                 const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
                                 const int* tile_seq, const int* tile_q0, int n_tiles, int q_heads, int kv_heads,
-                                int dim, int page_tokens, float scale, int window, cudaStream_t stream) {
+                                int dim, int page_tokens, float scale, int window, int vdim, const float* sinks,
+                                const float* gates, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (dim <= 0 || dim > MAX_DIM || dim % 4 || kv_heads <= 0 || q_heads % kv_heads || q_heads > 65535) return LB_ERR_SIZE;
-  const size_t smem = (size_t)(BQ * dim + BKEYS * (dim + 1) + BKEYS * dim) * sizeof(float);
+  if (vdim <= 0 || vdim > MAX_DIM || vdim % 4) return LB_ERR_SIZE;
+  // q rows, key rows padded by one float, value rows (16-byte aligned: both sizes are multiples of 4)
+  const size_t smem = (size_t)(BQ * dim + BKEYS * (dim + 1) + BKEYS * vdim) * sizeof(float);
   dim3 grid(n_tiles, q_heads);
   if (dtype == LB_F32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(paged_attention_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     lb_launch(paged_attention_simt_kernel<float>, grid, WARPS * 32, smem, stream, 
         (const float*)q, (const float*)k_pool, (const float*)v_pool, (float*)out, block_table, table_width, cu_q,
-        ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window);
+        ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates);
   } else if (dtype == LB_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(paged_attention_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     lb_launch(paged_attention_simt_kernel<bf16>, grid, WARPS * 32, smem, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window);
+        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates);
   } else
     return LB_ERR_DTYPE;
   return lb_last_error();

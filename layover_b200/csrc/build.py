@@ -34,6 +34,7 @@ SOURCES: dict[str, tuple[str, tuple[str, ...]]] = {
     "elementwise": ("elementwise.cu", ()),
     "gemm_simt": ("gemm_simt.cu", ()),
     "attention_simt": ("attention_simt.cu", ()),
+    "linear_attention": ("linear_attention.cu", ()),
     "sampling": ("sampling.cu", ()),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ()),
     "attention_mma": ("attention_mma.cu", ()),

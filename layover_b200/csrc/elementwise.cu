@@ -32,6 +32,37 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
   }
 }
 
+// The same gather into a 32-bit residual stream: x[t, :] = float(table[id, :]).
+template <typename T>
+__global__ void embed_wide_kernel(const int* __restrict__ ids, const int* __restrict__ token_src,
+                                  const int* __restrict__ records, const T* __restrict__ table, float* __restrict__ x,
+                                  int hidden, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
+  int id = ids[blockIdx.x];
+  if (token_src && records) {
+    const int slot = token_src[blockIdx.x];
+    if (slot >= 0) id = records[(size_t)slot * LB_RECORD_WORDS + LB_RECORD_LAST_TOKEN];
+  }
+  id = min(max(id, 0), vocab - 1);
+  const T* src = table + (size_t)id * hidden;
+  float* dst = x + (size_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = Elem<T>::load(src + i);
+}
+
+LB_EXPORT int lb_embed_wide(int dtype, const int* ids, const int* token_src, const int* records, const void* table,
+                            float* x, int tokens, int hidden, int vocab, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (vocab <= 0) return LB_ERR_SIZE;
+  if (dtype == LB_F32)
+    lb_launch(embed_wide_kernel<float>, tokens, 256, 0, stream, ids, token_src, records, (const float*)table, x, hidden, vocab);
+  else if (dtype == LB_BF16)
+    lb_launch(embed_wide_kernel<bf16>, tokens, 256, 0, stream, ids, token_src, records, (const bf16*)table, x, hidden, vocab);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
 LB_EXPORT int lb_embed(int dtype, const int* ids, const int* token_src, const int* records, const void* table, void* x,
                        int tokens, int hidden, int vocab, cudaStream_t stream) {
   if (tokens <= 0) return 0;
@@ -431,7 +462,12 @@ LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool
 // product each round to T (layover/model.py:152-153).
 // `block` 0: the row is [all gates | all ups]. `block` b > 0: gates and ups alternate in blocks of b
 // features ([b gates | b ups | b gates | ...]), the layout of the products' fused epilogue.
-template <typename T, bool VEC>
+// ACT 0: silu (above); ACT 1: relu (max(z, 0), exact in T, so only the product rounds).
+template <int ACT> __device__ __forceinline__ float gate_activation(float g) {
+  return ACT == 1 ? fmaxf(g, 0.f) : g / (1.0f + expf(-g));
+}
+
+template <typename T, bool VEC, int ACT = 0>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long total, int inter, int block) {
   pdl_launch_dependents();
   pdl_wait();
@@ -447,15 +483,15 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     Pack<T>::load(gp, g);
     Pack<T>::load(gp + up_at, u);
 #pragma unroll
-    for (int i = 0; i < Pack<T>::N; ++i) g[i] = Elem<T>::round(g[i] / (1.0f + expf(-g[i]))) * u[i];
+    for (int i = 0; i < Pack<T>::N; ++i) g[i] = Elem<T>::round(gate_activation<ACT>(g[i])) * u[i];
     Pack<T>::store(out + idx, g);
   } else {
     const float g = Elem<T>::load(gp), u = Elem<T>::load(gp + up_at);
-    Elem<T>::store(out + idx, Elem<T>::round(g / (1.0f + expf(-g))) * u);
+    Elem<T>::store(out + idx, Elem<T>::round(gate_activation<ACT>(g)) * u);
   }
 }
 
-template <typename T>
+template <typename T, int ACT = 0>
 static int launch_swiglu(const void* gate_up, void* out, long total, int inter, int block, cudaStream_t stream) {
   constexpr int N = Pack<T>::N;
   const bool vec = inter % N == 0 && (block == 0 || block % N == 0) && (uintptr_t)gate_up % 16 == 0 &&
@@ -463,8 +499,8 @@ static int launch_swiglu(const void* gate_up, void* out, long total, int inter, 
   const int threads = 256;
   const long work = vec ? total / N : total;
   const unsigned blocks = (unsigned)((work + threads - 1) / threads);
-  if (vec) lb_launch(swiglu_kernel<T, true>, blocks, threads, 0, stream, (const T*)gate_up, (T*)out, total, inter, block);
-  else lb_launch(swiglu_kernel<T, false>, blocks, threads, 0, stream, (const T*)gate_up, (T*)out, total, inter, block);
+  if (vec) lb_launch(swiglu_kernel<T, true, ACT>, blocks, threads, 0, stream, (const T*)gate_up, (T*)out, total, inter, block);
+  else lb_launch(swiglu_kernel<T, false, ACT>, blocks, threads, 0, stream, (const T*)gate_up, (T*)out, total, inter, block);
   return lb_last_error();
 }
 
@@ -476,4 +512,166 @@ LB_EXPORT int lb_swiglu(int dtype, const void* gate_up, void* out, int tokens, i
   if (dtype == LB_F32) return launch_swiglu<float>(gate_up, out, total, inter, block, stream);
   if (dtype == LB_BF16) return launch_swiglu<bf16>(gate_up, out, total, inter, block, stream);
   return LB_ERR_DTYPE;
+}
+
+// The same gated product with the activation named by the caller: act 0 silu, 1 relu.
+LB_EXPORT int lb_gated_act(int dtype, const void* gate_up, void* out, int tokens, int inter, int block, int act,
+                           cudaStream_t stream) {
+  const long total = (long)tokens * inter;
+  if (total <= 0) return 0;
+  if (block < 0 || (block > 0 && inter % block) || act < 0 || act > 1) return LB_ERR_SIZE;
+  if (dtype == LB_F32)
+    return act ? launch_swiglu<float, 1>(gate_up, out, total, inter, block, stream)
+               : launch_swiglu<float, 0>(gate_up, out, total, inter, block, stream);
+  if (dtype == LB_BF16)
+    return act ? launch_swiglu<bf16, 1>(gate_up, out, total, inter, block, stream)
+               : launch_swiglu<bf16, 0>(gate_up, out, total, inter, block, stream);
+  return LB_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------- 32-bit residual stream: (normed) add + RMSNorm
+// For models whose residual stream stays in 32-bit floats whatever the run's type T, and whose
+// sub-layers' outputs are RMS-normed before they are added (a norm before and after each sub-layer):
+//   v      = x[row] + delta[row] * s + extra[row]
+//            s = delta_w * rsqrt(mean(delta[row]^2) + delta_eps) per channel (delta_w null: s = 1);
+//            delta and extra may each be null
+//   x[row] = v                                         (not with `rows`: then x is only read)
+//   out[r] = T(weight * v * rsqrt(mean(v^2) + eps))    (weight null: no output, only the sum)
+// Everything is computed in 32-bit and rounded once, at the store of out. One block per row; the
+// block size depends on the width only, so a row's sums do not depend on the batch.
+template <typename T>
+__global__ void residual_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                        const float* __restrict__ delta_w, float delta_eps,
+                                        const float* __restrict__ extra, const float* __restrict__ weight,
+                                        T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+  extern __shared__ float row_vals[];  // hidden floats + 33 for the reductions
+  pdl_launch_dependents();
+  pdl_wait();
+  float* scratch = row_vals + hidden;
+  const size_t src = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+  float* xr = x + src * hidden;
+  const T* dr = delta ? delta + src * hidden : nullptr;
+  const float* er = extra ? extra + src * hidden : nullptr;
+  float dinv = 1.f;
+  if (dr && delta_w) {
+    float ds = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float d = Elem<T>::load(dr + i);
+      ds += d * d;
+    }
+    ds = block_sum(ds, scratch);
+    dinv = 1.0f / sqrtf(ds / (float)hidden + delta_eps);
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = xr[i];
+    if (dr) v += delta_w ? Elem<T>::load(dr + i) * dinv * delta_w[i] : Elem<T>::load(dr + i);
+    if (er) v += er[i];
+    if (!rows && (dr || er)) xr[i] = v;
+    row_vals[i] = v;
+    ss += v * v;
+  }
+  if (!weight) return;
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  T* o = out + (size_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) Elem<T>::store(o + i, weight[i] * (row_vals[i] * inv));
+}
+
+template <typename T>
+static int launch_residual_rmsnorm(float* x, const void* delta, const float* delta_w, float delta_eps, const float* extra,
+                                   const float* weight, void* out, const int* rows, int n_rows, int hidden, float eps,
+                                   cudaStream_t stream) {
+  static LbPerDeviceOnce once;
+  const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+  if (smem > 200 * 1024) return LB_ERR_SIZE;
+  if (smem > 48 * 1024 && once.first())
+    cudaFuncSetAttribute(residual_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  lb_launch(residual_rmsnorm_kernel<T>, n_rows, threads, smem, stream, x, (const T*)delta, delta_w, delta_eps, extra, weight,
+            (T*)out, rows, hidden, eps);
+  return lb_last_error();
+}
+
+LB_EXPORT int lb_residual_rmsnorm(int dtype, float* x, const void* delta, const float* delta_w, float delta_eps,
+                                  const float* extra, const float* weight, void* out, const int* rows, int n_rows,
+                                  int hidden, float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (hidden <= 0 || (weight && !out)) return LB_ERR_SIZE;
+  if (dtype == LB_F32)
+    return launch_residual_rmsnorm<float>(x, delta, delta_w, delta_eps, extra, weight, out, rows, n_rows, hidden, eps, stream);
+  if (dtype == LB_BF16)
+    return launch_residual_rmsnorm<bf16>(x, delta, delta_w, delta_eps, extra, weight, out, rows, n_rows, hidden, eps, stream);
+  return LB_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------- whole-row QK-norm + KV write + head gates
+// For attention whose q and k are RMS-normed over the whole projection (all heads at once, one
+// weight per channel) and are not rotated. A token's row of the stacked projection is
+//   [ q: q_heads * dim | k: kv_heads * dim | v: kv_heads * vdim | gate logits: q_heads (optional) ].
+//   q_out[t]  = T(q * rsqrt(mean(q^2) + eps) * q_w)          (q_w null: q is copied)
+//   k page    = T(k * rsqrt(mean(k^2) + eps) * k_w),  v page = v
+//               k_pool[((page * kv_heads + g) * page_tokens + slot) * dim + c], v_pool likewise with vdim,
+//               page * page_tokens + slot = slot_map[t]
+//   gates[t, h] = 1 / (1 + exp(-logit_h))  in 32-bit          (gates null: the row has no logits)
+// One block per token; statistics in 32-bit.
+template <typename T>
+__global__ void qk_rownorm_kv_kernel(const T* __restrict__ proj, long row_stride, T* __restrict__ q_out,
+                                     T* __restrict__ k_pool, T* __restrict__ v_pool, const float* __restrict__ q_w,
+                                     const float* __restrict__ k_w, const int* __restrict__ slot_map,
+                                     float* __restrict__ gates, int q_heads, int kv_heads, int dim, int vdim,
+                                     int page_tokens, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, nq = q_heads * dim, nk = kv_heads * dim, nv = kv_heads * vdim;
+  const T* row = proj + (size_t)t * row_stride;
+  float qinv = 1.f, kinv = 1.f;
+  if (q_w) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = Elem<T>::load(row + i); s += v * v; }
+    qinv = 1.0f / sqrtf(block_sum(s, scratch) / (float)nq + eps);
+  }
+  if (k_w) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = Elem<T>::load(row + nq + i); s += v * v; }
+    kinv = 1.0f / sqrtf(block_sum(s, scratch) / (float)nk + eps);
+  }
+  T* qo = q_out + (size_t)t * nq;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+    const float v = Elem<T>::load(row + i);
+    Elem<T>::store(qo + i, q_w ? v * qinv * q_w[i] : v);
+  }
+  const int slot = slot_map[t];
+  const size_t page = (size_t)(slot / page_tokens), in_page = (size_t)(slot % page_tokens);
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+    const int g = i / dim, c = i - g * dim;
+    const float v = Elem<T>::load(row + nq + i);
+    Elem<T>::store(k_pool + ((page * kv_heads + g) * page_tokens + in_page) * dim + c, k_w ? v * kinv * k_w[i] : v);
+  }
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const int g = i / vdim, c = i - g * vdim;
+    v_pool[((page * kv_heads + g) * page_tokens + in_page) * vdim + c] = row[nq + nk + i];
+  }
+  if (gates)
+    for (int h = threadIdx.x; h < q_heads; h += blockDim.x)
+      gates[(size_t)t * q_heads + h] = 1.0f / (1.0f + expf(-Elem<T>::load(row + nq + nk + nv + h)));
+}
+
+LB_EXPORT int lb_qk_rownorm_kv(int dtype, const void* proj, long row_stride, void* q_out, void* k_pool, void* v_pool,
+                               const float* q_w, const float* k_w, const int* slot_map, float* gates, int tokens,
+                               int q_heads, int kv_heads, int dim, int vdim, int page_tokens, float eps,
+                               cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (q_heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || page_tokens <= 0) return LB_ERR_SIZE;
+  const int threads = q_heads * dim >= 1024 ? 256 : 128;
+  if (dtype == LB_F32)
+    lb_launch(qk_rownorm_kv_kernel<float>, tokens, threads, 0, stream, (const float*)proj, row_stride, (float*)q_out,
+              (float*)k_pool, (float*)v_pool, q_w, k_w, slot_map, gates, q_heads, kv_heads, dim, vdim, page_tokens, eps);
+  else if (dtype == LB_BF16)
+    lb_launch(qk_rownorm_kv_kernel<bf16>, tokens, threads, 0, stream, (const bf16*)proj, row_stride, (bf16*)q_out,
+              (bf16*)k_pool, (bf16*)v_pool, q_w, k_w, slot_map, gates, q_heads, kv_heads, dim, vdim, page_tokens, eps);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
 }

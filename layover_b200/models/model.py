@@ -8,6 +8,8 @@ functions, one per kind of step; here one serves every mix). It reads nothing ba
 
 from __future__ import annotations
 
+import contextlib
+
 import torch
 
 from .. import ops
@@ -15,6 +17,8 @@ from .. import profiling
 from ..parts.base import Runtime, build_part, walk_parts
 from ..weights.loader import TensorSpec
 from .spec import ModelSpec
+
+_NO_RANGE = contextlib.nullcontext()
 
 
 class Model:
@@ -26,6 +30,9 @@ class Model:
         self.embedding = self.head = None
         self.runtime: Runtime | None = None
         self._range_names = [f"layer{e.layer}" for e in spec.schedule]
+        self._keeps_embedding = any(e.adds_embedding for e in spec.schedule)
+        if self._keeps_embedding and spec.residual_dtype != "float32":
+            raise ValueError("adding the embedding output between passes needs a 32-bit residual stream")
 
     # ---- weights
     def tensor_specs(self) -> list[TensorSpec]:
@@ -93,20 +100,26 @@ class Model:
         return tuple(sorted(set(sizes)))
 
     # ---- one step
-    def forward(self, batch, cache) -> torch.Tensor:
+    def forward(self, batch, cache, observe=None) -> torch.Tensor:
+        """`observe(entry index, x, delta)`, if given, is called after every schedule entry with the
+        residual stream and the entry's not-yet-added output (tensors that later entries overwrite:
+        copy what is to be kept). It is for tests and debugging; no step of the engine passes it."""
         rt = self.runtime
         batch.shared.clear()    # what parts share within a step (rotary tables) is made anew by every run
-        x = torch.empty((batch.n_tokens, self.spec.hidden_size), dtype=rt.dtype, device=rt.device)
+        stream_dtype = torch.float32 if self.spec.residual_dtype == "float32" else rt.dtype
+        x = torch.empty((batch.n_tokens, self.spec.hidden_size), dtype=stream_dtype, device=rt.device)
         records = getattr(cache, "records", None)      # tokens the host has not seen yet come from the requests' records
         ops.embed(batch.token_ids, self.embedding, x, batch.token_src if records is not None else None, records)
+        embedded = x.clone() if self._keeps_embedding else None     # the stream is updated in place
         delta = None
-        if profiling.active():
-            for index, entry in enumerate(self.spec.schedule):
-                with profiling.nvtx_range(self._range_names[index]):
+        for index, entry in enumerate(self.spec.schedule):
+            with profiling.nvtx_range(self._range_names[index]) if profiling.active() else _NO_RANGE:
+                if entry.adds_embedding:
+                    x, delta = self.blocks[entry.layer].forward(x, delta, batch, cache.view(index), extra=embedded)
+                else:
                     x, delta = self.blocks[entry.layer].forward(x, delta, batch, cache.view(index))
-        else:
-            for index, entry in enumerate(self.spec.schedule):
-                x, delta = self.blocks[entry.layer].forward(x, delta, batch, cache.view(index))
+            if observe is not None:
+                observe(index, x, delta)
         if batch.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
         h = self.final_norm.forward(x, delta, rows=batch.logit_rows)

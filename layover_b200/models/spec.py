@@ -3,7 +3,9 @@
 `ModelSpec` is what an architecture's `build_spec(config)` returns. Nothing in it is specific
 to one architecture: layers may differ from one another (each names its own block and parts),
 and `schedule` is a list that may run a layer twice or let an entry attend over the pages that
-an earlier entry wrote.
+an earlier entry wrote; every entry has a cache or state of its own unless it says otherwise. An
+entry may also ask for the embedding output to be added to the stream before it runs (models
+that run a span of layers several times feed the input in again before each further pass).
 """
 
 from __future__ import annotations
@@ -24,6 +26,7 @@ class LayerSpec:
 class ScheduleEntry:
     layer: int                       # index into ModelSpec.layers
     reads_cache_of: int | None = None  # index of an earlier schedule entry whose pages this one reads
+    adds_embedding: bool = False       # the embedding output is added to the stream right before this entry
 
 
 @dataclass
@@ -41,6 +44,7 @@ class ModelSpec:
     init_std: float = 0.02
     init_norm_std: float = 0.0
     ignorable_tensors: frozenset = frozenset()
+    residual_dtype: str | None = None   # "float32": the residual stream is 32-bit whatever the run's type
 
     def __post_init__(self):
         if not self.schedule:

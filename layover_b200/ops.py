@@ -84,16 +84,20 @@ RECORD_POSITION, RECORD_SEED_LO, RECORD_SEED_HI, RECORD_COUNT, RECORD_TEMPERATUR
 
 def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, token_src: torch.Tensor | None = None,
           records: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t] = table[id]; ids int32 [T], table [V, H], out [T, H]. Where token_src[t] >= 0 the id is the
-    last token in row token_src[t] of `records` (int32 [slots, RECORD_WORDS]) instead of ids[t]."""
-    _need(ids, torch.int32, "ids"); _need(table, None, "table"); _need(out, table.dtype, "out")
+    """out[t] = table[id]; ids int32 [T], table [V, H], out [T, H] of the table's type, or float32 (a
+    32-bit residual stream). Where token_src[t] >= 0 the id is the last token in row token_src[t] of
+    `records` (int32 [slots, RECORD_WORDS]) instead of ids[t]."""
+    _need(ids, torch.int32, "ids"); _need(table, None, "table")
+    wide = out.dtype == torch.float32 and table.dtype != torch.float32     # a 32-bit residual stream over a narrower table
+    _need(out, torch.float32 if wide else table.dtype, "out")
     if (token_src is None) != (records is None):
         raise ValueError("embed: token_src and records come together")
     if token_src is not None:
         _need(token_src, torch.int32, "token_src"); _need(records, torch.int32, "records")
         if records.dim() != 2 or records.shape[1] != RECORD_WORDS or token_src.shape[0] != ids.shape[0]:
             raise ValueError("embed: records must be [slots, RECORD_WORDS] and token_src one entry per token")
-    fn = _fn("elementwise", "lb_embed", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    fn = _fn("elementwise", "lb_embed_wide" if wide else "lb_embed",
+             [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(fn(dtype_code(table.dtype), _ptr(ids), _ptr(token_src), _ptr(records), _ptr(table), _ptr(out), ids.shape[0],
               table.shape[1], table.shape[0], _stream()), "embed")
     return out
@@ -117,6 +121,81 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
     _check(fn(dtype_code(x.dtype), _ptr(x), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n_rows, x.shape[-1],
               float(eps), _stream()), "add_rmsnorm")
     return out
+
+
+def residual_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, delta_weight: torch.Tensor | None, delta_eps: float,
+                     extra: torch.Tensor | None, weight: torch.Tensor | None, eps: float, out: torch.Tensor | None,
+                     rows: torch.Tensor | None = None) -> torch.Tensor | None:
+    """The add + RMSNorm of a 32-bit residual stream x (float32 [T, H], updated in place unless `rows`
+    picks source rows):
+
+        x += delta * delta_weight * rsqrt(mean(delta^2) + delta_eps)     (delta_weight None: x += delta)
+        x += extra                                                       (float32 [T, H], e.g. the embedding output)
+        out = weight * x * rsqrt(mean(x^2) + eps)                        (weight None: no output)
+
+    delta and out are in the run's type (bfloat16 or float32); all arithmetic is 32-bit."""
+    _need(x, torch.float32, "x")
+    hidden = x.shape[-1]
+    run = out.dtype if out is not None else (delta.dtype if delta is not None else torch.float32)
+    if delta is not None:
+        _need(delta, run, "delta")
+        if delta.shape != x.shape:
+            raise ValueError("residual_rmsnorm: delta must have x's shape")
+    for name, t in (("delta_weight", delta_weight), ("weight", weight)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.shape[0] != hidden:
+                raise ValueError(f"residual_rmsnorm: {name} must have one entry per channel")
+    if extra is not None:
+        _need(extra, torch.float32, "extra")
+        if extra.shape != x.shape:
+            raise ValueError("residual_rmsnorm: extra must have x's shape")
+    n_rows = x.shape[0] if rows is None else rows.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    if (weight is None) != (out is None) or (out is not None and (out.shape[0] < n_rows or out.shape[-1] != hidden)):
+        raise ValueError("residual_rmsnorm: weight and out come together, out [rows, H]")
+    if out is not None:
+        _need(out, run, "out")
+    fn = _fn("elementwise", "lb_residual_rmsnorm",
+             [c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+              c_void_p])
+    _check(fn(dtype_code(run), _ptr(x), _ptr(delta), _ptr(delta_weight), float(delta_eps), _ptr(extra), _ptr(weight),
+              _ptr(out), _ptr(rows), n_rows, hidden, float(eps), _stream()), "residual_rmsnorm")
+    return out
+
+
+def qk_rownorm_kv(proj: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                  q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None, slot_map: torch.Tensor,
+                  gates: torch.Tensor | None, q_heads: int, kv_heads: int, dim: int, vdim: int, page_tokens: int,
+                  eps: float) -> None:
+    """RMSNorm of q and of k over the whole projection (all heads at once, a weight per channel), no
+    rotation; q to q_out, k and v to their pages, sigmoid of the per-head gate logits to `gates`.
+
+    proj [T, >= q_heads*dim + kv_heads*(dim + vdim) (+ q_heads)], rows may be padded; q_out [T, q_heads*dim];
+    k_pool [pages, kv_heads, page_tokens, dim]; v_pool [pages, kv_heads, page_tokens, vdim]; gates float32 [T, q_heads]."""
+    _need(q_out, proj.dtype, "q_out"); _need(k_pool, proj.dtype, "k_pool"); _need(v_pool, proj.dtype, "v_pool")
+    _need(slot_map, torch.int32, "slot_map")
+    tokens = proj.shape[0]
+    used = q_heads * dim + kv_heads * (dim + vdim) + (q_heads if gates is not None else 0)
+    if proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[1] < used or tuple(q_out.shape) != (tokens, q_heads * dim):
+        raise ValueError("qk_rownorm_kv: the projection row does not hold these heads")
+    if tuple(k_pool.shape[1:]) != (kv_heads, page_tokens, dim) or tuple(v_pool.shape[1:]) != (kv_heads, page_tokens, vdim):
+        raise ValueError("qk_rownorm_kv: the pools do not match the heads")
+    for name, t, n in (("q_norm_w", q_norm_w, q_heads * dim), ("k_norm_w", k_norm_w, kv_heads * dim)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != n:
+                raise ValueError(f"qk_rownorm_kv: {name} must have {n} entries")
+    if gates is not None:
+        _need(gates, torch.float32, "gates")
+        if tuple(gates.shape) != (tokens, q_heads):
+            raise ValueError("qk_rownorm_kv: gates must be [tokens, q_heads]")
+    fn = _fn("elementwise", "lb_qk_rownorm_kv",
+             [c_int, c_void_p, c_long] + [c_void_p] * 7 + [c_int] * 6 + [c_float, c_void_p])
+    _check(fn(dtype_code(proj.dtype), _ptr(proj), proj.stride(0), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_norm_w),
+              _ptr(k_norm_w), _ptr(slot_map), _ptr(gates), tokens, q_heads, kv_heads, dim, vdim, page_tokens, float(eps),
+              _stream()), "qk_rownorm_kv")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -172,6 +251,69 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> torch.Te
     return out
 
 
+GATE_ACTIVATIONS = {"silu": 0, "relu": 1}
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str, block: int = 0) -> torch.Tensor:
+    """out = act(gate) * up with act "silu" or "relu"; layouts as `swiglu`."""
+    _need(gate_up, None, "gate_up"); _need(out, gate_up.dtype, "out")
+    inter = gate_up.shape[1] // 2
+    if gate_up.shape[1] != 2 * inter or out.shape[1] != inter or out.shape[0] != gate_up.shape[0]:
+        raise ValueError("gated_act: shapes do not agree")
+    if activation not in GATE_ACTIVATIONS:
+        raise ValueError(f"gated_act: unknown activation {activation!r}")
+    fn = _fn("elementwise", "lb_gated_act", [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(gate_up.dtype), _ptr(gate_up), _ptr(out), gate_up.shape[0], inter, int(block),
+              GATE_ACTIVATIONS[activation], _stream()), "gated_act")
+    return out
+
+
+# ------------------------------------------------------------------ linear attention (a recurrence over state slots)
+SCAN_ACTIVATIONS = {None: 0, "none": 0, "silu": 1}
+
+
+def decay_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torch.Tensor, state: torch.Tensor,
+               cu_q: torch.Tensor, state_slots: torch.Tensor, decay: torch.Tensor, n_seqs: int, heads: int, dim: int,
+               vdim: int, activation: str | None = None) -> torch.Tensor:
+    """Per sequence and head S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over the step's tokens, from and
+    to the requests' state slots.
+
+    proj [T, N] holds q at column q_off (heads*dim), k at k_off, v at v_off (heads*vdim), each passed through
+    `activation` on the way in; out float32 [T, heads*vdim]; state float32 [slots, heads, dim, vdim];
+    decay float32 [heads]; cu_q int32 [S + 1]; state_slots int32 [S]."""
+    _need(out, torch.float32, "out"); _need(state, torch.float32, "state"); _need(decay, torch.float32, "decay")
+    _need(cu_q, torch.int32, "cu_q"); _need(state_slots, torch.int32, "state_slots")
+    tokens = proj.shape[0]
+    if proj.dim() != 2 or proj.stride(1) != 1 or max(q_off, k_off) + heads * dim > proj.shape[1] \
+            or v_off + heads * vdim > proj.shape[1] or min(q_off, k_off, v_off) < 0:
+        raise ValueError("decay_scan: the projection row does not hold these heads")
+    if tuple(out.shape) != (tokens, heads * vdim) or tuple(state.shape[1:]) != (heads, dim, vdim) or decay.numel() != heads:
+        raise ValueError("decay_scan: out, state or decay do not match the heads")
+    if activation not in SCAN_ACTIVATIONS:
+        raise ValueError(f"decay_scan: unknown activation {activation!r}")
+    fn = _fn("linear_attention", "lb_decay_scan",
+             [c_int, c_void_p, c_long, c_int, c_int, c_int] + [c_void_p] * 5 + [c_int] * 5 + [c_void_p])
+    _check(fn(dtype_code(proj.dtype), _ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(out), _ptr(state), _ptr(cu_q),
+              _ptr(state_slots), _ptr(decay), n_seqs, heads, dim, vdim, SCAN_ACTIVATIONS[activation], _stream()),
+           "decay_scan")
+    return out
+
+
+def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out = rmsnorm(x) * weight * sigmoid(gate): x float32 [T, n]; gate [T, n] in the run's type, a view into
+    wider rows is fine; out [T, n] in the run's type."""
+    _need(x, torch.float32, "x"); _need(weight, torch.float32, "weight"); _need(out, gate.dtype, "out")
+    tokens, n = x.shape
+    if gate.dim() != 2 or gate.stride(1) != 1 or tuple(gate.shape) != (tokens, n) or tuple(out.shape) != (tokens, n) \
+            or weight.numel() != n:
+        raise ValueError("gated_rmsnorm: shapes do not agree")
+    fn = _fn("linear_attention", "lb_gated_rmsnorm",
+             [c_int, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(fn(dtype_code(gate.dtype), _ptr(x), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), tokens, n, float(eps),
+              _stream()), "gated_rmsnorm")
+    return out
+
+
 # ------------------------------------------------------------------ matrix products
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[M, N] = a[M, K] @ w[N, K]^T with 32-bit FFMA accumulation (no tensor cores).
@@ -202,28 +344,46 @@ def attention_simt_block_queries() -> int:
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                    block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, tile_seq: torch.Tensor,
                    tile_q0: torch.Tensor, n_tiles: int, q_heads: int, kv_heads: int, dim: int, page_tokens: int,
-                   scale: float, window: int = 0) -> torch.Tensor:
+                   scale: float, window: int = 0, vdim: int | None = None, sinks: torch.Tensor | None = None,
+                   gates: torch.Tensor | None = None) -> torch.Tensor:
     """Paged causal attention in 32-bit arithmetic for any mix of segment lengths.
 
-    q, out [T, q_heads * dim]; pools [pages, kv_heads, page_tokens, dim]; block_table int32 [S, W];
-    cu_q int32 [S + 1]; ctx_len int32 [S]; (tile_seq, tile_q0) int32 [n_tiles] list the query tiles."""
+    q [T, q_heads * dim]; out [T, q_heads * vdim] (vdim defaults to dim); pools [pages, kv_heads, page_tokens,
+    dim or vdim]; block_table int32 [S, W]; cu_q int32 [S + 1]; ctx_len int32 [S]; (tile_seq, tile_q0) int32
+    [n_tiles] list the query tiles. `sinks` float32 [q_heads]: a score per head that joins the softmax's
+    denominator only; `gates` float32 [T, q_heads]: a factor on each head's output."""
+    vdim = dim if vdim is None else int(vdim)
     _need(q, None, "q"); _need(out, q.dtype, "out"); _need(k_pool, q.dtype, "k_pool"); _need(v_pool, q.dtype, "v_pool")
+    if tuple(out.shape) != (q.shape[0], q_heads * vdim) or k_pool.shape[-1] != dim or v_pool.shape[-1] != vdim:
+        raise ValueError("attention_simt: out or the pools do not match the head sizes")
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks")
+        if sinks.numel() != q_heads:
+            raise ValueError("attention_simt: one sink per query head")
+    if gates is not None:
+        _need(gates, torch.float32, "gates")
+        if tuple(gates.shape) != (q.shape[0], q_heads):
+            raise ValueError("attention_simt: gates must be [tokens, q_heads]")
     for name, t in (("block_table", block_table), ("cu_q", cu_q), ("ctx_len", ctx_len), ("tile_seq", tile_seq),
                     ("tile_q0", tile_q0)):
         _need(t, torch.int32, name)
     fn = _fn("attention_simt", "lb_attention_simt",
-             [c_int] + [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int] * 5 + [c_float, c_int, c_void_p])
+             [c_int] + [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int] * 5 + [c_float, c_int, c_int, c_void_p,
+                                                                                c_void_p, c_void_p])
     _check(fn(dtype_code(q.dtype), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
               block_table.shape[1], _ptr(cu_q), _ptr(ctx_len), _ptr(tile_seq), _ptr(tile_q0), n_tiles, q_heads,
-              kv_heads, dim, page_tokens, float(scale), int(window), _stream()), "attention_simt")
+              kv_heads, dim, page_tokens, float(scale), int(window), vdim, _ptr(sinks), _ptr(gates), _stream()),
+           "attention_simt")
     return out
 
 
-def attention_f32(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):
-    """The 32-bit path's attention for one step: one kernel for every mix of segment lengths."""
+def attention_f32(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window, vdim=None,
+                  sinks=None, gates=None):
+    """The 32-bit path's attention for one step: one kernel for every mix of segment lengths (and, in
+    either precision, the attention with sinks, head gates or values of another size than keys)."""
     tiles = batch.tiles[attention_simt_block_queries()]
     attention_simt(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq, tiles.tile_q0,
-                   tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)
+                   tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates)
 
 
 # ------------------------------------------------------------------ sampling

@@ -2,16 +2,18 @@ from .base import (
     PagedKVNeed, Part, PartSpec, Runtime, StateNeed, build_part, register_block, register_feed_forward,
     register_mixer, register_norm, register_position, registered, unregister, walk_parts,
 )
-from . import norm, position, feed_forward, attention, block  # noqa: F401  (fill the registries)
+from . import norm, position, feed_forward, attention, linear_attention, block  # noqa: F401  (fill the registries)
 from .attention import Attention, attention_spec
-from .block import PreNormBlock
+from .block import PreNormBlock, SandwichNormBlock
+from .linear_attention import DecayLinearAttention
 from .feed_forward import GatedMLP
-from .norm import RMSNorm
+from .norm import Deferred, RMSNorm
 from .position import RotaryHalf
 
 __all__ = [
     "PagedKVNeed", "Part", "PartSpec", "Runtime", "StateNeed", "build_part", "register_block",
     "register_feed_forward", "register_mixer", "register_norm", "register_position", "registered", "unregister",
     "walk_parts",
-    "Attention", "attention_spec", "PreNormBlock", "GatedMLP", "RMSNorm", "RotaryHalf",
+    "Attention", "attention_spec", "PreNormBlock", "SandwichNormBlock", "DecayLinearAttention", "GatedMLP", "Deferred",
+    "RMSNorm", "RotaryHalf",
 ]

@@ -30,7 +30,19 @@ class Attention(Part):
     its epilogue.
 
     The three projections are stacked at load into one [(q_heads + 2 kv_heads) head_dim, hidden]
-    matrix (the reference runs three products, layover/model.py:121-123)."""
+    matrix (the reference runs three products, layover/model.py:121-123).
+
+    Further options, for other designs than the reference's: `scale` (instead of 1/sqrt(head_dim));
+    `v_head_dim` (values of another size than keys); `qk_norm` = "whole" (ONE RMSNorm over the
+    whole q projection and one over the whole k projection, all heads at once, with a weight per
+    channel, instead of a norm per head); `sink` (tensor name: a learned score per query head that
+    joins the softmax's denominator and nothing else); `gate` (tensor name of a [q_heads, hidden]
+    matrix: head h's output is multiplied by sigmoid(gate h)_h before the output projection).
+    Any of these makes the part take its general path: the gate's rows are stacked under q, k, v
+    for one product, one kernel norms q and k over their whole rows, writes the pages and makes
+    the gates, and the attention runs in the kernel that keeps scores, weights and the weighted
+    sum in 32-bit in either precision (sinks, gates and the value size are its parameters). That
+    path has no rotation and no shared cache."""
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -39,21 +51,33 @@ class Attention(Part):
         self.hidden, self.q_heads, self.kv_heads, self.dim = (int(p[k]) for k in ("hidden", "q_heads", "kv_heads", "head_dim"))
         if self.q_heads % self.kv_heads:
             raise ValueError(f"q_heads ({self.q_heads}) must be divisible by kv_heads ({self.kv_heads})")
-        if self.dim % 16:
+        self.vdim = int(p.get("v_head_dim") or self.dim)
+        self.qk_norm = p.get("qk_norm", "per_head")
+        if self.qk_norm not in ("per_head", "whole"):
+            raise ValueError(f"qk_norm must be 'per_head' or 'whole', got {self.qk_norm!r}")
+        self.general = bool(self.vdim != self.dim or self.qk_norm == "whole" or p.get("sink") or p.get("gate"))
+        if self.general:
+            if self.dim % 4 or self.vdim % 4:
+                raise ValueError(f"head sizes must be multiples of 4, got {self.dim} and {self.vdim}")
+        elif self.dim % 16:
             raise ValueError(f"head_dim must be a multiple of 16, got {self.dim}")
-        if self.dim > 256:
-            raise ValueError(f"head_dim up to 256 is supported, got {self.dim}")
+        if max(self.dim, self.vdim) > 256:
+            raise ValueError(f"head sizes up to 256 are supported, got {max(self.dim, self.vdim)}")
         self.qk_norm_eps = p.get("qk_norm_eps")
         self.window = p.get("window")
         self.shares_cache = bool(p.get("shares_cache", False))
-        self.scale = float(p.get("scale", 1.0 / math.sqrt(self.dim)))
+        self.scale = float(p.get("scale") or 1.0 / math.sqrt(self.dim))
         self.position = build_part("position", p.get("position"), prefix)
+        if self.general and (self.shares_cache or self.position is not None):
+            raise ValueError("attention with sinks, gates, a whole-row norm or its own value size has no rotation "
+                             "and no shared cache")
         wanted = ["q", "o"] + ([] if self.shares_cache else ["k", "v"])
         if self.qk_norm_eps is not None:
             wanted += ["q_norm"] + ([] if self.shares_cache else ["k_norm"])
+        wanted += [k for k in ("sink", "gate") if p.get(k)]
         self.require(*wanted)
         self.names = {k: prefix + p[k] for k in wanted}
-        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = self.sink = None
         self._attend = self._project_heads = None
 
     # ---- what it wants
@@ -62,24 +86,30 @@ class Attention(Part):
         specs = [TensorSpec(n["q"], (self.q_heads * self.dim, self.hidden))]
         if not self.shares_cache:
             specs += [TensorSpec(n["k"], (self.kv_heads * self.dim, self.hidden)),
-                      TensorSpec(n["v"], (self.kv_heads * self.dim, self.hidden))]
-        specs.append(TensorSpec(n["o"], (self.hidden, self.q_heads * self.dim)))
+                      TensorSpec(n["v"], (self.kv_heads * self.vdim, self.hidden))]
+        specs.append(TensorSpec(n["o"], (self.hidden, self.q_heads * self.vdim)))
         if self.qk_norm_eps is not None:
-            specs.append(TensorSpec(n["q_norm"], (self.dim,), kind="vector", init="ones"))
+            whole = self.qk_norm == "whole"
+            specs.append(TensorSpec(n["q_norm"], (self.q_heads * self.dim if whole else self.dim,), kind="vector", init="ones"))
             if not self.shares_cache:
-                specs.append(TensorSpec(n["k_norm"], (self.dim,), kind="vector", init="ones"))
+                specs.append(TensorSpec(n["k_norm"], (self.kv_heads * self.dim if whole else self.dim,), kind="vector",
+                                        init="ones"))
+        if "sink" in n:
+            specs.append(TensorSpec(n["sink"], (self.q_heads,), kind="vector"))
+        if "gate" in n:
+            specs.append(TensorSpec(n["gate"], (self.q_heads, self.hidden)))
         if self.position is not None:
             specs += self.position.tensor_specs()
         return specs
 
     def cache_need(self):
-        return PagedKVNeed(self.kv_heads, self.dim, self.window)
+        return PagedKVNeed(self.kv_heads, self.dim, self.window, self.vdim if self.vdim != self.dim else None)
 
     def parts(self):
         return [self.position] if self.position is not None else []
 
     def kernel_libraries(self, dtype):
-        if dtype == torch.float32:
+        if dtype == torch.float32 or self.general:
             return ("elementwise", "attention_simt")
         names = ["elementwise", "attention_mma"]
         if ops.attention_tcgen05_takes_heads(self.q_heads, self.kv_heads, self.dim):
@@ -87,7 +117,7 @@ class Attention(Part):
         return tuple(names)
 
     def tile_sizes(self, dtype):
-        if dtype == torch.float32:
+        if dtype == torch.float32 or self.general:
             return (ops.attention_simt_block_queries(),)
         sizes = [ops.attention_mma_block_queries()]
         if ops.attention_tcgen05_takes_heads(self.q_heads, self.kv_heads, self.dim):
@@ -96,6 +126,8 @@ class Attention(Part):
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
+        if self.general:
+            return self._bind_general(tensors, runtime)
         if runtime.dtype == torch.float32:
             self._attend, self._project_heads = ops.attention_f32, None
         else:
@@ -113,8 +145,36 @@ class Attention(Part):
         if self.position is not None:
             self.position.bind(tensors, runtime)
 
+    def _bind_general(self, tensors, runtime):
+        n = self.names
+        rows = [tensors.pop(n["q"]), tensors.pop(n["k"]), tensors.pop(n["v"])]
+        if "gate" in n:
+            rows.append(tensors.pop(n["gate"]))
+        used = sum(r.shape[0] for r in rows)
+        if used % 16:           # whole 16-byte pieces per output row, whatever the head counts
+            rows.append(torch.zeros((16 - used % 16, self.hidden), dtype=rows[0].dtype, device=rows[0].device))
+        self.w_qkv = torch.cat(rows, dim=0).contiguous()
+        self.w_o = tensors[n["o"]]
+        if self.qk_norm_eps is not None:
+            self.q_norm_w, self.k_norm_w = tensors[n["q_norm"]], tensors[n["k_norm"]]
+        self.sink = tensors[n["sink"]] if "sink" in n else None
+
+    def _forward_general(self, h, batch, cache):
+        tokens, group = h.shape[0], batch.groups[cache.group]
+        proj = self.runtime.linear(h, self.w_qkv)
+        q = torch.empty((tokens, self.q_heads * self.dim), dtype=h.dtype, device=h.device)
+        gates = torch.empty((tokens, self.q_heads), dtype=torch.float32, device=h.device) if "gate" in self.names else None
+        ops.qk_rownorm_kv(proj, q, cache.k_pool, cache.v_pool, self.q_norm_w, self.k_norm_w, group.slot_map, gates,
+                          self.q_heads, self.kv_heads, self.dim, self.vdim, cache.page_tokens, float(self.qk_norm_eps or 0.0))
+        out = torch.empty((tokens, self.q_heads * self.vdim), dtype=h.dtype, device=h.device)
+        ops.attention_f32(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.dim, cache.page_tokens,
+                          self.scale, self.window or 0, self.vdim, self.sink, gates)
+        return self.runtime.linear(out, self.w_o)
+
     # ---- one step
     def forward(self, h: torch.Tensor, batch, cache) -> torch.Tensor:
+        if self.general:
+            return self._forward_general(h, batch, cache)
         q = self.project(h, batch, cache)
         out = torch.empty_like(q)
         self.attend(q, cache, batch, batch.groups[cache.group], out)

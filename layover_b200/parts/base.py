@@ -14,16 +14,20 @@ What each kind must offer:
                   parts() -> [Part]                   its own sub-parts (default: none)
                   kernel_libraries(dtype) -> names    kernel libraries it launches (default: none)
                   tile_sizes(dtype) -> sizes          query-tile lists it wants in a batch (default: none)
-  norm            forward(x, delta, rows=None) -> h   x += delta in place (delta may be None), h = norm(x);
-                                                      with rows, only those rows, x untouched
+  norm            forward(x, delta, rows=None, extra=None) -> h
+                                                      x += delta in place (delta may be None, or a sub-layer's
+                                                      output that is still to be normed: `Deferred`), h = norm(x);
+                                                      with rows, only those rows, x untouched; extra: one more
+                                                      tensor to add (the embedding output between passes)
   position        tables(batch) -> float32 [T, 2, dim/2] cos/sin of the step, or None; made once per
                                                       step and kept in batch.shared (the fused kernel applies it)
                   apply(q, k, positions)              when tables() is None: rotate q [T, heads, dim], k in place
   mixer           cache_need() -> PagedKVNeed | StateNeed | None
                   forward(h, batch, cache) -> [T, hidden]     cache is the view it was given for its need
   feed-forward    forward(h) -> [T, hidden]
-  block           forward(x, delta, batch, cache) -> (x, delta)   the residual stream and the
-                                                      not-yet-added output of the last sub-layer
+  block           forward(x, delta, batch, cache, extra=None) -> (x, delta)   the residual stream and the
+                                                      not-yet-added output of the last sub-layer; extra is
+                                                      added to the stream before the block's first norm
 """
 
 from __future__ import annotations
@@ -47,14 +51,20 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """Keys and values of every token (window None) or of the last `window` tokens, in pages."""
+    """Keys and values of every token (window None) or of the last `window` tokens, in pages.
+    `v_head_dim`: the size of a value where it differs from a key's (None: the same)."""
     kv_heads: int
     head_dim: int
     window: int | None = None
+    v_head_dim: int | None = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
     def elements_per_token(self) -> int:
         """Pool elements one token takes in one layer with this need (keys and values)."""
-        return 2 * self.kv_heads * self.head_dim
+        return self.kv_heads * (self.head_dim + self.value_dim)
 
 
 @dataclass(frozen=True)

@@ -2,8 +2,12 @@
 
 from __future__ import annotations
 
+import contextlib
+
 from .. import profiling
 from .base import Part, build_part, register_block
+
+_NO_RANGE = contextlib.nullcontext()
 
 
 @register_block("pre_norm")
@@ -38,15 +42,66 @@ class PreNormBlock(Part):
     def cache_need(self):
         return self.mixer.cache_need()
 
-    def forward(self, x, delta, batch, cache):
+    def forward(self, x, delta, batch, cache, extra=None):
         if profiling.active():
             with profiling.nvtx_range("mixer"):
-                h = self.input_norm.forward(x, delta)
+                h = self.input_norm.forward(x, delta, extra=extra)
                 attended = self.mixer.forward(h, batch, cache)
             with profiling.nvtx_range("feed_forward"):
                 h = self.post_norm.forward(x, attended)
                 return x, self.feed_forward.forward(h)
-        h = self.input_norm.forward(x, delta)
+        h = self.input_norm.forward(x, delta, extra=extra)
         attended = self.mixer.forward(h, batch, cache)
         h = self.post_norm.forward(x, attended)
         return x, self.feed_forward.forward(h)
+
+
+@register_block("sandwich_norm")
+class SandwichNormBlock(Part):
+    """A norm before AND after each sub-layer: x = x + mixer_out_norm(mixer(input_norm(x))), then, where
+    the layer has a feed-forward, x = x + ff_out_norm(feed_forward(post_norm(x))).
+
+    As in the pre-norm block nothing is added here: a sub-layer's output is handed on as
+    `norm.defer(output)` and the next norm of the stream (this block's, the next block's or the
+    model's final one) norms it, adds it and norms the sum in one kernel.
+
+    params: input_norm, mixer, mixer_out_norm (PartSpecs); post_norm, feed_forward, ff_out_norm
+    (PartSpecs, or all three None for a layer without a feed-forward)."""
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.require("input_norm", "mixer", "mixer_out_norm")
+        self.input_norm = build_part("norm", params["input_norm"], prefix)
+        self.mixer = build_part("mixer", params["mixer"], prefix)
+        self.mixer_out_norm = build_part("norm", params["mixer_out_norm"], prefix)
+        second = [params.get(k) for k in ("post_norm", "feed_forward", "ff_out_norm")]
+        if any(p is None for p in second) and any(p is not None for p in second):
+            raise ValueError("sandwich_norm: post_norm, feed_forward and ff_out_norm come together or not at all")
+        self.post_norm = build_part("norm", second[0], prefix)
+        self.feed_forward = build_part("feed_forward", second[1], prefix)
+        self.ff_out_norm = build_part("norm", second[2], prefix)
+
+    def parts(self):
+        return [p for p in (self.input_norm, self.mixer, self.mixer_out_norm, self.post_norm, self.feed_forward,
+                            self.ff_out_norm) if p is not None]
+
+    def tensor_specs(self):
+        return [spec for part in self.parts() for spec in part.tensor_specs()]
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        for part in self.parts():
+            part.bind(tensors, runtime)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, x, delta, batch, cache, extra=None):
+        with profiling.nvtx_range("mixer") if profiling.active() else _NO_RANGE:
+            h = self.input_norm.forward(x, delta, extra=extra)
+            mixed = self.mixer_out_norm.defer(self.mixer.forward(h, batch, cache))
+        if self.feed_forward is None:
+            return x, mixed
+        with profiling.nvtx_range("feed_forward") if profiling.active() else _NO_RANGE:
+            h = self.post_norm.forward(x, mixed)
+            return x, self.ff_out_norm.defer(self.feed_forward.forward(h))

@@ -11,20 +11,22 @@ from .base import Part, register_feed_forward
 
 @register_feed_forward("gated_mlp")
 class GatedMLP(Part):
-    """down(act(gate(x)) * up(x)) without bias (layover/model.py:145-153); act = silu.
+    """down(act(gate(x)) * up(x)) without bias (layover/model.py:145-153); act = silu or relu.
 
-    params: hidden, inter, activation ("silu"), gate, up, down (tensor names relative to the
+    params: hidden, inter, activation ("silu", the default, or "relu"), gate, up, down (tensor names relative to the
     prefix). gate and up are stacked at load into one [2 inter, hidden] matrix so that one
     product reads x once. In a bfloat16 run whose width allows it, the rows are interleaved for
     the tensor-core product with the activation in its epilogue and no [T, 2 inter] tensor is ever
-    written; otherwise the activation kernel reads both halves of its row."""
+    written; otherwise the activation kernel reads both halves of its row. The product's epilogue
+    knows silu only: with relu the interleaved product is followed by the activation kernel."""
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
         self.require("hidden", "inter", "gate", "up", "down")
         self.hidden, self.inter = int(params["hidden"]), int(params["inter"])
-        if params.get("activation", "silu") != "silu":
-            raise ValueError(f"gated_mlp: unsupported activation {params['activation']!r}")
+        self.activation = params.get("activation", "silu")
+        if self.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"gated_mlp: unsupported activation {self.activation!r}")
         self.names = {k: prefix + params[k] for k in ("gate", "up", "down")}
         self.gate_up = self.down = None
 
@@ -54,15 +56,20 @@ class GatedMLP(Part):
         which is faster there (a whole feed-forward at 64 tokens: 41.7 us against 43.5 us fused)."""
         tokens = h.shape[0]
         out = torch.empty((tokens, self.inter), dtype=torch.bfloat16, device=h.device)
-        if (tokens > 128 or tokens <= 16) and ops.gemm_tcgen05_supports(h, self.gate_up):
+        if self.activation == "silu" and (tokens > 128 or tokens <= 16) and ops.gemm_tcgen05_supports(h, self.gate_up):
             return ops.gemm_tcgen05(h, self.gate_up, out, epilogue="swiglu")
         gate_up = self.runtime.linear(h, self.gate_up)
-        return ops.swiglu(gate_up, out, block=ops.SWIGLU_BLOCK)
+        if self.activation == "silu":
+            return ops.swiglu(gate_up, out, block=ops.SWIGLU_BLOCK)
+        return ops.gated_act(gate_up, out, self.activation, block=ops.SWIGLU_BLOCK)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         if self.fused:
             return self.runtime.linear(self.activated(h), self.down)
         gate_up = self.runtime.linear(h, self.gate_up)
         act = torch.empty((h.shape[0], self.inter), dtype=h.dtype, device=h.device)
-        ops.swiglu(gate_up, act)
+        if self.activation == "silu":
+            ops.swiglu(gate_up, act)
+        else:
+            ops.gated_act(gate_up, act, self.activation)
         return self.runtime.linear(act, self.down)

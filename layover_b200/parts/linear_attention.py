@@ -1,0 +1,81 @@
+"""Linear attention: a recurrence over a state of fixed size per request instead of keys and values
+of every token."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorSpec
+from .base import Part, StateNeed, register_mixer
+
+
+@register_mixer("decay_linear_attention")
+class DecayLinearAttention(Part):
+    """q, k (heads x head_dim) and v (heads x v_head_dim) are projections passed through an
+    activation; per head the state S [head_dim, v_head_dim] follows
+
+        S_t = decay_h S_(t-1) + k_t v_t^T,      o_t = S_t^T q_t
+
+    with one constant decay per head and no other scale. The heads' outputs, side by side, are
+    RMS-normed together (one weight per channel), multiplied by sigmoid(gate h) channel by channel
+    and projected. The state is 32-bit, starts at zero and lives in the request's state slot; the
+    recurrence, its decay and the norm are computed in 32-bit in either precision.
+
+    params: hidden, heads, head_dim, v_head_dim, decay (one number, or one per head), norm_eps,
+    activation ("silu" or None); tensor names q, k, v, gate, o, norm relative to the prefix.
+
+    One kernel walks a sequence's tokens of the step in order, whether they are a prompt, a portion
+    or a single token, so the result does not depend on the cut. The four projections are stacked
+    at load into one matrix and read from the product's rows in place."""
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.require("hidden", "heads", "head_dim", "v_head_dim", "decay", "norm_eps", "q", "k", "v", "gate", "o", "norm")
+        p = params
+        self.hidden, self.heads, self.dim, self.vdim = (int(p[k]) for k in ("hidden", "heads", "head_dim", "v_head_dim"))
+        if self.dim > 256:
+            raise ValueError(f"head_dim up to 256 is supported, got {self.dim}")
+        decay = p["decay"]
+        self.decay_values = [float(d) for d in decay] if isinstance(decay, (list, tuple)) else [float(decay)] * self.heads
+        if len(self.decay_values) != self.heads:
+            raise ValueError(f"decay must be one number or one per head ({self.heads}), got {len(self.decay_values)}")
+        self.norm_eps = float(p["norm_eps"])
+        self.activation = p.get("activation", "silu")
+        if self.activation not in ops.SCAN_ACTIVATIONS:
+            raise ValueError(f"unsupported activation {self.activation!r}")
+        self.names = {k: prefix + p[k] for k in ("q", "k", "v", "gate", "o", "norm")}
+        self.w_in = self.w_o = self.norm_w = self.decay = None
+
+    def tensor_specs(self):
+        n, qk, vv = self.names, self.heads * self.dim, self.heads * self.vdim
+        return [TensorSpec(n["q"], (qk, self.hidden)), TensorSpec(n["k"], (qk, self.hidden)),
+                TensorSpec(n["v"], (vv, self.hidden)), TensorSpec(n["gate"], (vv, self.hidden)),
+                TensorSpec(n["o"], (self.hidden, vv)), TensorSpec(n["norm"], (vv,), kind="vector", init="ones")]
+
+    def cache_need(self):
+        return StateNeed((self.heads, self.dim, self.vdim), torch.float32)
+
+    def kernel_libraries(self, dtype):
+        return ("linear_attention",)
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.names
+        rows = [tensors.pop(n["q"]), tensors.pop(n["k"]), tensors.pop(n["v"]), tensors.pop(n["gate"])]
+        used = sum(r.shape[0] for r in rows)
+        if used % 16:           # whole 16-byte pieces per output row
+            rows.append(torch.zeros((16 - used % 16, self.hidden), dtype=rows[0].dtype, device=rows[0].device))
+        self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.w_o, self.norm_w = tensors[n["o"]], tensors[n["norm"]]
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=runtime.device)
+
+    def forward(self, h: torch.Tensor, batch, cache) -> torch.Tensor:
+        tokens, qk, vv = h.shape[0], self.heads * self.dim, self.heads * self.vdim
+        proj = self.runtime.linear(h, self.w_in)                    # [T, q | k | v | gate (| padding)]
+        scanned = torch.empty((tokens, vv), dtype=torch.float32, device=h.device)
+        ops.decay_scan(proj, 0, qk, 2 * qk, scanned, cache.state, batch.cu_q, batch.state_slots, self.decay, batch.n_seqs,
+                       self.heads, self.dim, self.vdim, self.activation)
+        gated = torch.empty((tokens, vv), dtype=h.dtype, device=h.device)
+        ops.gated_rmsnorm(scanned, proj[:, 2 * qk + vv: 2 * qk + 2 * vv], self.norm_w, self.norm_eps, gated)
+        return self.runtime.linear(gated, self.w_o)

@@ -36,7 +36,7 @@ def parse_args(argv=None):
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at a time (each rounded up to 64)")
     parser.add_argument("--block-tokens", type=int, default=16, help="tokens per page (must divide 64)")
-    parser.add_argument("--max-requests", type=int, default=16, help="most requests live at a time")
+    parser.add_argument("--max-requests", type=int, default=4, help="state slots: most requests live at a time")
     parser.add_argument("--cuda-graphs", action="store_true",
                         help="replay steps of single tokens from captured CUDA graphs, as serving does")
     return parser.parse_args(argv)
