@@ -146,7 +146,10 @@ __device__ __forceinline__ void ldmatrix_x4_trans_at(uint32_t (&r)[4], uint32_t 
 // MAX_DIM and every address offset is a constant. UPPER false skips the softmax of rows 8..15
 // (decode with at most 8 query heads per KV head). `masked` false skips the comparisons for a
 // tile that every row sees completely. Scores stay unscaled; the scale enters the exponent.
-template <int MAX_DIM, bool EXACT, int PAIRS, bool UPPER>
+// SPLIT: a weight enters the second product as the sum of two bfloat16 numbers (its rounded value and
+// the rounded rest), each multiplied exactly and added in 32-bit: the weights keep 16 bits of
+// mantissa instead of 8, at one more MMA per step of P V.
+template <int MAX_DIM, bool EXACT, int PAIRS, bool UPPER, bool SPLIT = false>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[MAX_DIM / 16][4], uint32_t k_addr, uint32_t v_addr,
                                           int dim, float (&o)[MAX_DIM / 8][4], float (&m_run)[2], float (&l_run)[2],
                                           bool masked, int key0, int p0, int p1, int key_lo, int window, float c,
@@ -226,17 +229,21 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[MAX_DIM / 16][4],
   }
   float tile_sum[2] = {0.f, 0.f};
   uint32_t pf[PAIRS][4];
+  uint32_t pl[SPLIT ? PAIRS : 1][4];     // the rests
 #pragma unroll
   for (int n = 0; n < NT_S; ++n) {
     const float e0 = fast_exp2(fmaf(s[n][0], c, neg_base[0])), e1 = fast_exp2(fmaf(s[n][1], c, neg_base[0]));
     tile_sum[0] += e0 + e1;
     pf[n >> 1][(n & 1) * 2] = pack_bf16(e0, e1);
+    if (SPLIT) pl[n >> 1][(n & 1) * 2] = pack_bf16(e0 - Elem<bf16>::round(e0), e1 - Elem<bf16>::round(e1));
     if (UPPER) {
       const float e2 = fast_exp2(fmaf(s[n][2], c, neg_base[1])), e3 = fast_exp2(fmaf(s[n][3], c, neg_base[1]));
       tile_sum[1] += e2 + e3;
       pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(e2, e3);
+      if (SPLIT) pl[n >> 1][(n & 1) * 2 + 1] = pack_bf16(e2 - Elem<bf16>::round(e2), e3 - Elem<bf16>::round(e3));
     } else {
       pf[n >> 1][(n & 1) * 2 + 1] = 0u;
+      if (SPLIT) pl[n >> 1][(n & 1) * 2 + 1] = 0u;
     }
   }
   l_run[0] = l_run[0] * alpha[0] + tile_sum[0];
@@ -261,6 +268,10 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[MAX_DIM / 16][4],
         if (EXACT || n0 + u < dk) {
           mma_bf16(o[2 * (n0 + u)], pf[kk], b[u][0], b[u][1]);
           mma_bf16(o[2 * (n0 + u) + 1], pf[kk], b[u][2], b[u][3]);
+          if (SPLIT) {
+            mma_bf16(o[2 * (n0 + u)], pl[kk], b[u][0], b[u][1]);
+            mma_bf16(o[2 * (n0 + u) + 1], pl[kk], b[u][2], b[u][3]);
+          }
         }
       }
     }
@@ -268,13 +279,17 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[MAX_DIM / 16][4],
 }
 
 // ------------------------------------------------------------------------------- prefill
-template <int MAX_DIM, bool EXACT>
+// SINK: the variant for attention with a sink per head (`sinks`, natural-log units: it joins the
+// denominator only), a 32-bit gate per (token, head) on the output (`gates`), either may be null, and
+// weights that keep 16 bits of mantissa in the second product (SPLIT above).
+template <int MAX_DIM, bool EXACT, bool SINK = false>
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                          bf16* __restrict__ out, const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int q_heads, int kv_heads,
-                         int dim_arg, int page_tokens, float scale_log2, int window, int chunk_shift, int page_shift) {
+                         int dim_arg, int page_tokens, float scale_log2, int window, int chunk_shift, int page_shift,
+                         const float* __restrict__ sinks, const float* __restrict__ gates) {
   constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int dim = EXACT ? MAX_DIM : dim_arg;
@@ -348,8 +363,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
       // every row of the warp sees the whole tile unless it reaches past the first row's position,
       // starts before the first visible key or a window cuts it
       const bool masked = tile * BKEYS + BKEYS - 1 > p_warp || tile * BKEYS < key_lo || window > 0;
-      warp_tile<MAX_DIM, EXACT, BKEYS / 16, true>(qf, k_base + buf * buf_bytes, v_base + buf * buf_bytes, dim, o, m_run,
-                                                  l_run, masked, tile * BKEYS, p0, p1, key_lo, window, scale_log2, t);
+      warp_tile<MAX_DIM, EXACT, BKEYS / 16, true, SINK>(qf, k_base + buf * buf_bytes, v_base + buf * buf_bytes, dim, o, m_run,
+                                                        l_run, masked, tile * BKEYS, p0, p1, key_lo, window, scale_log2, t);
     }
     __syncthreads();   // the buffer may be overwritten by the next iteration's prefetch
   }
@@ -363,7 +378,12 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
   for (int r = 0; r < 2; ++r) {
     const int row = warp * 16 + g + 8 * r;
     if (row >= n_q) continue;
-    const float inv = 1.0f / l_run[r];
+    float inv = 1.0f / l_run[r];
+    if (SINK) {
+      // the row's maximum is finite (a query sees itself); scores are unscaled, the sink is not to be scaled
+      if (sinks) inv = 1.0f / (l_run[r] + fast_exp2(sinks[head] * 1.4426950408889634f - m_run[r] * scale_log2));
+      if (gates) inv *= gates[(size_t)(row0 + q0 + row) * q_heads + head];
+    }
     bf16* dst = out + ((size_t)(row0 + q0 + row) * q_heads + head) * dim;
 #pragma unroll
     for (int n = 0; n < NT_O; ++n) {
@@ -386,14 +406,16 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 // flight); with two a block is slower but three blocks share an SM instead of two, which wins once a
 // launch has more blocks than two per SM can hold at once (12 warps an SM hide the MMAs' latency
 // better than 8; measured at 64 sequences of 3,072 keys: 148 us against 158 us).
-template <int MAX_DIM, bool EXACT, bool UPPER, bool CLUSTER = false, int STAGES = 3>
+// SINK: as in the prefill kernel; the sink joins the denominator once, where the splits have been merged.
+template <int MAX_DIM, bool EXACT, bool UPPER, bool CLUSTER = false, int STAGES = 3, bool SINK = false>
 __global__ void __launch_bounds__(THREADS, STAGES == 2 ? 3 : 2)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                         bf16* __restrict__ out, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                         const int* __restrict__ seq_list, int q_heads, int kv_heads, int dim_arg, int page_tokens,
                         float scale_log2, int window, int splits, float* __restrict__ partials,
-                        unsigned* __restrict__ counters, int chunk_shift, int page_shift) {
+                        unsigned* __restrict__ counters, int chunk_shift, int page_shift,
+                        const float* __restrict__ sinks, const float* __restrict__ gates) {
   constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int dim = EXACT ? MAX_DIM : dim_arg;
@@ -482,8 +504,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     }
     // only the tile that holds the last key, or the first visible one, needs the comparisons
     const bool masked = tile * BKEYS + BKEYS - 1 > p || tile * BKEYS < key_lo;
-    warp_tile<MAX_DIM, EXACT, 1, UPPER>(qf, k_base + buf * buf_bytes, v_base + buf * buf_bytes, dim, o, m_run, l_run, masked,
-                                        tile * BKEYS + warp * 16, p, p, key_lo, 0, scale_log2, t);
+    warp_tile<MAX_DIM, EXACT, 1, UPPER, SINK>(qf, k_base + buf * buf_bytes, v_base + buf * buf_bytes, dim, o, m_run, l_run,
+                                              masked, tile * BKEYS + warp * 16, p, p, key_lo, 0, scale_log2, t);
     __syncthreads();
   }
   cp_async_wait<0>();
@@ -508,6 +530,14 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   }
   __syncthreads();
   const float c = scale_log2;
+  // what a row's merged sums become: the sink joins the denominator (its exponent against the same
+  // base as the scores'), the gate multiplies the quotient
+  auto finish = [&](float acc, float l_all, float base, int r) -> float {
+    if (SINK && sinks) l_all += fast_exp2(sinks[head0 + r] * 1.4426950408889634f - base * c);
+    float value = l_all > 0.f ? acc / l_all : 0.f;
+    if (SINK && gates) value *= gates[(size_t)row * q_heads + head0 + r];
+    return value;
+  };
   if (CLUSTER) {
     const int total = group * dim, per = (total + splits - 1) / splits;
     float* recv_acc = merge + (size_t)WARPS * 16 * mstride;            // [splits][per]: this block's share, from every split
@@ -551,7 +581,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         acc += recv_acc[(size_t)s2 * per + k] * f;
         l_all += recv_ml[((size_t)s2 * group + r) * 2 + 1] * f;
       }
-      out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+      out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(finish(acc, l_all, base, r));
     }
     return;
   }
@@ -572,7 +602,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
       l_all += src[dim + 1] * f;
     }
     if (splits == 1) {
-      out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+      out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(finish(acc, l_all, base, r));
     } else {
       my_partial[r * mstride + col] = acc;
       if (col == 0) { my_partial[r * mstride + dim] = m_all; my_partial[r * mstride + dim + 1] = l_all; }
@@ -611,6 +641,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
       factor[s * group + r] = f;
       l_all += l_part[s * group + r] * f;
     }
+    if (SINK && sinks) l_all += fast_exp2(sinks[head0 + r] * 1.4426950408889634f - base * c);
     l_total[r] = l_all;
   }
   __syncthreads();
@@ -619,7 +650,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     float acc = 0.f;
 #pragma unroll 8
     for (int s = 0; s < splits; ++s) acc += all[((size_t)s * group + r) * mstride + col] * factor[s * group + r];
-    out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(l_total[r] > 0.f ? acc / l_total[r] : 0.f);
+    float value = l_total[r] > 0.f ? acc / l_total[r] : 0.f;
+    if (SINK && gates) value *= gates[(size_t)row * q_heads + head0 + r];
+    out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(value);
   }
   if (threadIdx.x == 0) counters[tile_id] = 0;
 }
@@ -663,6 +696,23 @@ void configure_once() {      // once per device: the attribute belongs to the de
   cudaGetLastError();
   allow_smem(attention_decode_kernel<128, true, false, false, 2>, decode_smem(128, 2));
   allow_smem(attention_decode_kernel<128, true, false, true, 2>, decode_smem(128, 2));
+  allow_smem(attention_prefill_kernel<128, true, true>, prefill_smem(128));
+  allow_smem(attention_prefill_kernel<128, false, true>, prefill_smem(128));
+  allow_smem(attention_prefill_kernel<256, true, true>, prefill_smem(256));
+  allow_smem(attention_prefill_kernel<256, false, true>, prefill_smem(256));
+  allow_smem(attention_decode_kernel<128, true, true, false, 3, true>, decode_smem(128));
+  allow_smem(attention_decode_kernel<128, false, true, false, 3, true>, decode_smem(128));
+  allow_smem(attention_decode_kernel<256, true, true, false, 3, true>, decode_smem(256));
+  allow_smem(attention_decode_kernel<256, false, true, false, 3, true>, decode_smem(256));
+}
+
+// the variants with sinks, gates and split weights: three stages, merged through scratch memory
+template <typename... Args>
+int launch_decode_sink(int dim, dim3 grid, size_t smem, cudaStream_t stream, Args... args) {
+  if (dim == 128) return lb_launch(attention_decode_kernel<128, true, true, false, 3, true>, grid, dim3(THREADS), smem, stream, args...);
+  if (dim < 128) return lb_launch(attention_decode_kernel<128, false, true, false, 3, true>, grid, dim3(THREADS), smem, stream, args...);
+  if (dim == 256) return lb_launch(attention_decode_kernel<256, true, true, false, 3, true>, grid, dim3(THREADS), smem, stream, args...);
+  return lb_launch(attention_decode_kernel<256, false, true, false, 3, true>, grid, dim3(THREADS), smem, stream, args...);
 }
 
 // launches the decode kernel instantiation for this head size and group
@@ -697,9 +747,11 @@ int launch_decode_cluster(int group, dim3 grid, size_t smem, cudaStream_t stream
 LB_EXPORT int lb_attention_prefill_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
                                         const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
                                         const int* tile_seq, const int* tile_q0, int n_tiles, int q_heads, int kv_heads,
-                                        int dim, int page_tokens, float scale, int window, cudaStream_t stream) {
+                                        int dim, int page_tokens, float scale, int window, const float* sinks,
+                                        const float* gates, int exact_weights, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (dim <= 0 || dim % 16 || dim > 256 || kv_heads <= 0 || q_heads % kv_heads || q_heads > 65535) return LB_ERR_SIZE;
+  const bool sink = sinks || gates || exact_weights;
   configure_once();
   const size_t smem = prefill_smem(dim);
   const float scale_log2 = scale * 1.4426950408889634f;
@@ -707,8 +759,14 @@ LB_EXPORT int lb_attention_prefill_bf16(const void* q, const void* k_pool, const
   dim3 grid(n_tiles, q_heads), block(THREADS);
   int code;
 #define LB_PREFILL_ARGS (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, \
-                        ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window, chunk_shift, page_shift
-  if (dim == 128) code = lb_launch(attention_prefill_kernel<128, true>, grid, block, smem, stream, LB_PREFILL_ARGS);
+                        ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window, chunk_shift, page_shift, \
+                        sinks, gates
+  if (sink) {
+    if (dim == 128) code = lb_launch(attention_prefill_kernel<128, true, true>, grid, block, smem, stream, LB_PREFILL_ARGS);
+    else if (dim < 128) code = lb_launch(attention_prefill_kernel<128, false, true>, grid, block, smem, stream, LB_PREFILL_ARGS);
+    else if (dim == 256) code = lb_launch(attention_prefill_kernel<256, true, true>, grid, block, smem, stream, LB_PREFILL_ARGS);
+    else code = lb_launch(attention_prefill_kernel<256, false, true>, grid, block, smem, stream, LB_PREFILL_ARGS);
+  } else if (dim == 128) code = lb_launch(attention_prefill_kernel<128, true>, grid, block, smem, stream, LB_PREFILL_ARGS);
   else if (dim < 128) code = lb_launch(attention_prefill_kernel<128, false>, grid, block, smem, stream, LB_PREFILL_ARGS);
   else if (dim == 256) code = lb_launch(attention_prefill_kernel<256, true>, grid, block, smem, stream, LB_PREFILL_ARGS);
   else code = lb_launch(attention_prefill_kernel<256, false>, grid, block, smem, stream, LB_PREFILL_ARGS);
@@ -731,7 +789,7 @@ LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const 
                                        const int* seq_list, int n_seqs, int q_heads, int kv_heads, int dim,
                                        int page_tokens, float scale, int window, int splits, float* partials,
                                        long partial_floats, unsigned* counters, int n_counters, int stages,
-                                       cudaStream_t stream) {
+                                       const float* sinks, const float* gates, int exact_weights, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (dim <= 0 || dim % 16 || dim > 256 || kv_heads <= 0 || q_heads % kv_heads || q_heads / kv_heads > 16 ||
       kv_heads > 65535 || splits < 1 || splits > 65535)
@@ -741,33 +799,39 @@ LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const 
     return LB_ERR_SIZE;
   configure_once();
   // two K/V stages (three blocks an SM) exist for the served head size with at most 8 heads per KV head
-  const bool two_stages = stages == 2 && dim == 128 && q_heads / kv_heads <= 8;
+  const bool sink = sinks || gates || exact_weights;
+  const bool two_stages = !sink && stages == 2 && dim == 128 && q_heads / kv_heads <= 8;
   const size_t smem = decode_smem(dim, two_stages ? 2 : 3);
   if ((3 * (size_t)splits + 1) * (q_heads / kv_heads) * sizeof(float) > smem) return LB_ERR_SIZE;   // merge factors
   const float scale_log2 = scale * 1.4426950408889634f;
   const int chunk_shift = (dim >> 3) <= THREADS ? exact_log2(dim >> 3) : -1, page_shift = exact_log2(page_tokens);
   dim3 grid(n_seqs, kv_heads, splits);
   int code;
-  if (two_stages) {
+  const float* no_floats = nullptr;
+  if (sink) {
+    code = launch_decode_sink(dim, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
+                              block_table, table_width, cu_q, ctx_len, seq_list, q_heads, kv_heads, dim, page_tokens,
+                              scale_log2, window, splits, partials, counters, chunk_shift, page_shift, sinks, gates);
+  } else if (two_stages) {
     if (decode_cluster_fits(dim, q_heads / kv_heads, splits, smem))
       code = lb_launch_cluster(attention_decode_kernel<128, true, false, true, 2>, grid, dim3(THREADS), smem, stream, grid.z,
                                (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width,
                                cu_q, ctx_len, seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits,
-                               (float*)nullptr, (unsigned*)nullptr, chunk_shift, page_shift);
+                               (float*)nullptr, (unsigned*)nullptr, chunk_shift, page_shift, no_floats, no_floats);
     else
       code = lb_launch(attention_decode_kernel<128, true, false, false, 2>, grid, dim3(THREADS), smem, stream, (const bf16*)q,
                        (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
                        q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters, chunk_shift,
-                       page_shift);
+                       page_shift, no_floats, no_floats);
   } else if (decode_cluster_fits(dim, q_heads / kv_heads, splits, smem))
     code = launch_decode_cluster(q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
                                  (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
                                  q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, (float*)nullptr,
-                                 (unsigned*)nullptr, chunk_shift, page_shift);
+                                 (unsigned*)nullptr, chunk_shift, page_shift, no_floats, no_floats);
   else
     code = launch_decode(dim, q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
                          (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
                          q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters,
-                         chunk_shift, page_shift);
+                         chunk_shift, page_shift, no_floats, no_floats);
   return code ? code : lb_last_error();
 }

@@ -611,16 +611,19 @@ LB_EXPORT int lb_residual_rmsnorm(int dtype, float* x, const void* delta, const 
 //   [ q: q_heads * dim | k: kv_heads * dim | v: kv_heads * vdim | gate logits: q_heads (optional) ].
 //   q_out[t]  = T(q * rsqrt(mean(q^2) + eps) * q_w)          (q_w null: q is copied)
 //   k page    = T(k * rsqrt(mean(k^2) + eps) * k_w),  v page = v
-//               k_pool[((page * kv_heads + g) * page_tokens + slot) * dim + c], v_pool likewise with vdim,
+//               k_pool[((page * kv_heads + g) * page_tokens + slot) * k_room + c], v_pool likewise with v_room,
 //               page * page_tokens + slot = slot_map[t]
 //   gates[t, h] = 1 / (1 + exp(-logit_h))  in 32-bit          (gates null: the row has no logits)
+// A head may have more room where it is written than it has channels (q_room >= dim per head of q_out,
+// k_room >= dim and v_room >= vdim per page row: kernels that want keys and values of one size); the
+// rest of the room is filled with zeros, which change no score and no weighted sum.
 // One block per token; statistics in 32-bit.
 template <typename T>
 __global__ void qk_rownorm_kv_kernel(const T* __restrict__ proj, long row_stride, T* __restrict__ q_out,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, const float* __restrict__ q_w,
                                      const float* __restrict__ k_w, const int* __restrict__ slot_map,
                                      float* __restrict__ gates, int q_heads, int kv_heads, int dim, int vdim,
-                                     int page_tokens, float eps) {
+                                     int page_tokens, float eps, int q_room, int k_room, int v_room) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
@@ -637,21 +640,31 @@ __global__ void qk_rownorm_kv_kernel(const T* __restrict__ proj, long row_stride
     for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = Elem<T>::load(row + nq + i); s += v * v; }
     kinv = 1.0f / sqrtf(block_sum(s, scratch) / (float)nk + eps);
   }
-  T* qo = q_out + (size_t)t * nq;
-  for (int i = threadIdx.x; i < nq; i += blockDim.x) {
-    const float v = Elem<T>::load(row + i);
-    Elem<T>::store(qo + i, q_w ? v * qinv * q_w[i] : v);
+  T* qo = q_out + (size_t)t * q_heads * q_room;
+  for (int i = threadIdx.x; i < q_heads * q_room; i += blockDim.x) {
+    const int h = i / q_room, c = i - h * q_room;
+    float v = 0.f;
+    if (c < dim) {
+      v = Elem<T>::load(row + h * dim + c);
+      if (q_w) v = v * qinv * q_w[h * dim + c];
+    }
+    Elem<T>::store(qo + i, v);
   }
   const int slot = slot_map[t];
   const size_t page = (size_t)(slot / page_tokens), in_page = (size_t)(slot % page_tokens);
-  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
-    const int g = i / dim, c = i - g * dim;
-    const float v = Elem<T>::load(row + nq + i);
-    Elem<T>::store(k_pool + ((page * kv_heads + g) * page_tokens + in_page) * dim + c, k_w ? v * kinv * k_w[i] : v);
+  for (int i = threadIdx.x; i < kv_heads * k_room; i += blockDim.x) {
+    const int g = i / k_room, c = i - g * k_room;
+    float v = 0.f;
+    if (c < dim) {
+      v = Elem<T>::load(row + nq + g * dim + c);
+      if (k_w) v = v * kinv * k_w[g * dim + c];
+    }
+    Elem<T>::store(k_pool + ((page * kv_heads + g) * page_tokens + in_page) * k_room + c, v);
   }
-  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-    const int g = i / vdim, c = i - g * vdim;
-    v_pool[((page * kv_heads + g) * page_tokens + in_page) * vdim + c] = row[nq + nk + i];
+  for (int i = threadIdx.x; i < kv_heads * v_room; i += blockDim.x) {
+    const int g = i / v_room, c = i - g * v_room;
+    Elem<T>::store(v_pool + ((page * kv_heads + g) * page_tokens + in_page) * v_room + c,
+                   c < vdim ? Elem<T>::load(row + nq + nk + g * vdim + c) : 0.f);
   }
   if (gates)
     for (int h = threadIdx.x; h < q_heads; h += blockDim.x)
@@ -660,17 +673,21 @@ __global__ void qk_rownorm_kv_kernel(const T* __restrict__ proj, long row_stride
 
 LB_EXPORT int lb_qk_rownorm_kv(int dtype, const void* proj, long row_stride, void* q_out, void* k_pool, void* v_pool,
                                const float* q_w, const float* k_w, const int* slot_map, float* gates, int tokens,
-                               int q_heads, int kv_heads, int dim, int vdim, int page_tokens, float eps,
-                               cudaStream_t stream) {
+                               int q_heads, int kv_heads, int dim, int vdim, int page_tokens, float eps, int q_room,
+                               int k_room, int v_room, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (q_heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || page_tokens <= 0) return LB_ERR_SIZE;
+  if (q_heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || page_tokens <= 0 || q_room < dim || k_room < dim ||
+      v_room < vdim)
+    return LB_ERR_SIZE;
   const int threads = q_heads * dim >= 1024 ? 256 : 128;
   if (dtype == LB_F32)
     lb_launch(qk_rownorm_kv_kernel<float>, tokens, threads, 0, stream, (const float*)proj, row_stride, (float*)q_out,
-              (float*)k_pool, (float*)v_pool, q_w, k_w, slot_map, gates, q_heads, kv_heads, dim, vdim, page_tokens, eps);
+              (float*)k_pool, (float*)v_pool, q_w, k_w, slot_map, gates, q_heads, kv_heads, dim, vdim, page_tokens, eps,
+              q_room, k_room, v_room);
   else if (dtype == LB_BF16)
     lb_launch(qk_rownorm_kv_kernel<bf16>, tokens, threads, 0, stream, (const bf16*)proj, row_stride, (bf16*)q_out,
-              (bf16*)k_pool, (bf16*)v_pool, q_w, k_w, slot_map, gates, q_heads, kv_heads, dim, vdim, page_tokens, eps);
+              (bf16*)k_pool, (bf16*)v_pool, q_w, k_w, slot_map, gates, q_heads, kv_heads, dim, vdim, page_tokens, eps,
+              q_room, k_room, v_room);
   else
     return LB_ERR_DTYPE;
   return lb_last_error();

@@ -172,15 +172,19 @@ def qk_rownorm_kv(proj: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Tensor,
     """RMSNorm of q and of k over the whole projection (all heads at once, a weight per channel), no
     rotation; q to q_out, k and v to their pages, sigmoid of the per-head gate logits to `gates`.
 
-    proj [T, >= q_heads*dim + kv_heads*(dim + vdim) (+ q_heads)], rows may be padded; q_out [T, q_heads*dim];
-    k_pool [pages, kv_heads, page_tokens, dim]; v_pool [pages, kv_heads, page_tokens, vdim]; gates float32 [T, q_heads]."""
+    proj [T, >= q_heads*dim + kv_heads*(dim + vdim) (+ q_heads)], rows may be padded; q_out [T, q_heads*R];
+    k_pool [pages, kv_heads, page_tokens, R]; v_pool [pages, kv_heads, page_tokens, R]; gates float32 [T, q_heads].
+    R is each tensor's own room per head, at least dim (vdim for values): what is beyond the head's
+    channels is filled with zeros."""
     _need(q_out, proj.dtype, "q_out"); _need(k_pool, proj.dtype, "k_pool"); _need(v_pool, proj.dtype, "v_pool")
     _need(slot_map, torch.int32, "slot_map")
     tokens = proj.shape[0]
     used = q_heads * dim + kv_heads * (dim + vdim) + (q_heads if gates is not None else 0)
-    if proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[1] < used or tuple(q_out.shape) != (tokens, q_heads * dim):
+    if proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[1] < used or q_out.shape[0] != tokens or q_out.shape[1] % q_heads:
         raise ValueError("qk_rownorm_kv: the projection row does not hold these heads")
-    if tuple(k_pool.shape[1:]) != (kv_heads, page_tokens, dim) or tuple(v_pool.shape[1:]) != (kv_heads, page_tokens, vdim):
+    q_room, k_room, v_room = q_out.shape[1] // q_heads, k_pool.shape[-1], v_pool.shape[-1]
+    if tuple(k_pool.shape[1:3]) != (kv_heads, page_tokens) or tuple(v_pool.shape[1:3]) != (kv_heads, page_tokens) \
+            or q_room < dim or k_room < dim or v_room < vdim:
         raise ValueError("qk_rownorm_kv: the pools do not match the heads")
     for name, t, n in (("q_norm_w", q_norm_w, q_heads * dim), ("k_norm_w", k_norm_w, kv_heads * dim)):
         if t is not None:
@@ -192,10 +196,10 @@ def qk_rownorm_kv(proj: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Tensor,
         if tuple(gates.shape) != (tokens, q_heads):
             raise ValueError("qk_rownorm_kv: gates must be [tokens, q_heads]")
     fn = _fn("elementwise", "lb_qk_rownorm_kv",
-             [c_int, c_void_p, c_long] + [c_void_p] * 7 + [c_int] * 6 + [c_float, c_void_p])
+             [c_int, c_void_p, c_long] + [c_void_p] * 7 + [c_int] * 6 + [c_float, c_int, c_int, c_int, c_void_p])
     _check(fn(dtype_code(proj.dtype), _ptr(proj), proj.stride(0), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_norm_w),
               _ptr(k_norm_w), _ptr(slot_map), _ptr(gates), tokens, q_heads, kv_heads, dim, vdim, page_tokens, float(eps),
-              _stream()), "qk_rownorm_kv")
+              q_room, k_room, v_room, _stream()), "qk_rownorm_kv")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -627,19 +631,33 @@ def attention_mma_block_queries() -> int:
     return lib.lb_attention_mma_block_queries()
 
 
+def _sink_arguments(sinks, gates, tokens, q_heads, what):
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks")
+        if sinks.numel() != q_heads:
+            raise ValueError(f"{what}: one sink per query head")
+    if gates is not None:
+        _need(gates, torch.float32, "gates")
+        if tuple(gates.shape) != (tokens, q_heads):
+            raise ValueError(f"{what}: gates must be [tokens, q_heads]")
+
+
 def attention_prefill_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, tile_seq, tile_q0, n_tiles, q_heads,
-                           kv_heads, dim, page_tokens, scale, window=0):
-    """Tensor-core paged attention for prompt portions: tiles of 64 queries, any number of queries per sequence."""
+                           kv_heads, dim, page_tokens, scale, window=0, sinks=None, gates=None, exact_weights=False):
+    """Tensor-core paged attention for prompt portions: tiles of 64 queries, any number of queries per sequence.
+    `sinks` float32 [q_heads] join the softmax's denominator only, `gates` float32 [T, q_heads] multiply the
+    heads' outputs, `exact_weights` keeps 16 bits of the weights' mantissa in the second product."""
+    _sink_arguments(sinks, gates, q.shape[0], q_heads, "attention_prefill_bf16")
     for name, t in (("q", q), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
         _need(t, torch.bfloat16, name)
     for name, t in (("block_table", block_table), ("cu_q", cu_q), ("ctx_len", ctx_len), ("tile_seq", tile_seq),
                     ("tile_q0", tile_q0)):
         _need(t, torch.int32, name)
     fn = _fn("attention_mma", "lb_attention_prefill_bf16",
-             [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int] * 5 + [c_float, c_int, c_void_p])
+             [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int] * 5 + [c_float, c_int, c_void_p, c_void_p, c_int, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
               _ptr(ctx_len), _ptr(tile_seq), _ptr(tile_q0), n_tiles, q_heads, kv_heads, dim, page_tokens, float(scale),
-              int(window), _stream()), "attention_prefill_bf16")
+              int(window), _ptr(sinks), _ptr(gates), int(bool(exact_weights)), _stream()), "attention_prefill_bf16")
     return out
 
 
@@ -711,9 +729,11 @@ def decode_splits(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_contex
 
 
 def attention_decode_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, seq_list, n_seqs, q_heads, kv_heads, dim,
-                          page_tokens, scale, window=0, splits=1, stages=3):
+                          page_tokens, scale, window=0, splits=1, stages=3, sinks=None, gates=None, exact_weights=False):
     """Tensor-core paged attention for sequences with one new token each, the context split `splits` ways
-    (`stages` 2: the variant that fits three blocks an SM, see `decode_plan`)."""
+    (`stages` 2: the variant that fits three blocks an SM, see `decode_plan`). `sinks`, `gates` and
+    `exact_weights` as in `attention_prefill_bf16` (those variants merge their splits through scratch memory)."""
+    _sink_arguments(sinks, gates, q.shape[0], q_heads, "attention_decode_bf16")
     for name, t in (("q", q), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
         _need(t, torch.bfloat16, name)
     for name, t in (("block_table", block_table), ("cu_q", cu_q), ("ctx_len", ctx_len)):
@@ -723,11 +743,11 @@ def attention_decode_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, se
     partials, counters = attention_scratch(q.device)
     fn = _fn("attention_mma", "lb_attention_decode_bf16",
              [c_void_p] * 5 + [c_int] + [c_void_p] * 3 + [c_int] * 5 + [c_float, c_int, c_int, c_void_p, c_long, c_void_p,
-                                                                        c_int, c_int, c_void_p])
+                                                                        c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
               _ptr(ctx_len), _ptr(seq_list), n_seqs, q_heads, kv_heads, dim, page_tokens, float(scale), int(window),
-              int(splits), _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), int(stages), _stream()),
-           "attention_decode_bf16")
+              int(splits), _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), int(stages), _ptr(sinks),
+              _ptr(gates), int(bool(exact_weights)), _stream()), "attention_decode_bf16")
     return out
 
 
@@ -787,34 +807,42 @@ def attention_tcgen05_prefill(q, pool, layer, out, block_table, cu_q, ctx_len, t
     return out
 
 
-def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):
+def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window, sinks=None,
+                   gates=None, exact_weights=False):
     """The bfloat16 path's attention for one step: prompt portions go through the tcgen05 tile kernel
     where it takes the sizes (head size 128, pages of 8..128 tokens), else through the mma.sync
-    one; single tokens, alone or beside prompt portions, go through the split decode kernel."""
+    one; single tokens, alone or beside prompt portions, go through the split decode kernel. With
+    sinks, gates or exact weights the mma.sync kernels' variants for those run everywhere."""
+    plain = sinks is None and gates is None and not exact_weights
+    extras = dict(sinks=sinks, gates=gates, exact_weights=exact_weights)
+    # a window bounds the keys a single token reads, whatever its request's length
+    seen = (lambda ctx: min(ctx, window + 63)) if window else (lambda ctx: ctx)
     if batch.all_decode and q_heads // kv_heads <= 16:
         sms = gemm_scratch(q.device)[2]
         # planned for the step's own lengths; a captured step for its class of steps (the widest context
         # its block table can describe, with the mean that the class stands for)
         widest = min(batch.plan_max_ctx or block_table.shape[1] * page_tokens, block_table.shape[1] * page_tokens)
-        splits, stages = decode_plan(batch.n_seqs, q_heads, kv_heads, dim, widest, sms, batch.plan_mean_ctx or None)
+        mean = batch.plan_mean_ctx or None
+        splits, stages = decode_plan(batch.n_seqs, q_heads, kv_heads, dim, seen(widest), sms, seen(mean) if mean else None)
         attention_decode_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, None,
-                              batch.n_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits, stages)
+                              batch.n_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits, stages, **extras)
         return
     tiles_of = batch.tiles
     if batch.n_decode_seqs > 0 and q_heads // kv_heads <= 16:
         # a mixed step: the sequences with a single token go through the decode kernel (a tile kernel
         # would spend a whole tile of queries on each), the prompt portions through the tile kernel
         sms = gemm_scratch(q.device)[2]
-        splits, stages = decode_plan(batch.n_decode_seqs, q_heads, kv_heads, dim, batch.decode_max_ctx, sms,
-                                     batch.plan_mean_ctx or None)
+        mean = batch.plan_mean_ctx or None
+        splits, stages = decode_plan(batch.n_decode_seqs, q_heads, kv_heads, dim, seen(batch.decode_max_ctx), sms,
+                                     seen(mean) if mean else None)
         attention_decode_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, batch.decode_seqs,
-                              batch.n_decode_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits, stages)
+                              batch.n_decode_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits, stages, **extras)
         tiles_of = batch.portion_tiles
-    if cache.pool is not None and attention_tcgen05_supports(q_heads, kv_heads, dim, page_tokens):
+    if plain and cache.pool is not None and attention_tcgen05_supports(q_heads, kv_heads, dim, page_tokens):
         tiles = tiles_of[TCGEN05_TILE]
         attention_tcgen05_prefill(q, cache.pool, cache.layer, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq,
                                   tiles.tile_q0, tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)
         return
     tiles = tiles_of[attention_mma_block_queries()]
     attention_prefill_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq,
-                           tiles.tile_q0, tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)
+                           tiles.tile_q0, tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window, **extras)

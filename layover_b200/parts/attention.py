@@ -40,9 +40,12 @@ class Attention(Part):
     matrix: head h's output is multiplied by sigmoid(gate h)_h before the output projection).
     Any of these makes the part take its general path: the gate's rows are stacked under q, k, v
     for one product, one kernel norms q and k over their whole rows, writes the pages and makes
-    the gates, and the attention runs in the kernel that keeps scores, weights and the weighted
-    sum in 32-bit in either precision (sinks, gates and the value size are its parameters). That
-    path has no rotation and no shared cache."""
+    the gates, and the attention runs with sinks and gates as parameters of its kernels: in a float32
+    run the 32-bit kernel; in a bfloat16 run the tensor-core kernels (tiles for prompt portions,
+    the split kernel for single tokens) in their variant whose weights enter the second product with
+    16 bits of mantissa, where the head sizes are multiples of 16 (keys and values of different
+    sizes then share pages of the larger size, zero-filled: zeros change no score and no sum), and
+    the 32-bit kernel on bfloat16 pages otherwise. That path has no rotation and no shared cache."""
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -79,6 +82,7 @@ class Attention(Part):
         self.names = {k: prefix + p[k] for k in wanted}
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = self.sink = None
         self._attend = self._project_heads = None
+        self.room = None        # once bound: the size keys, values and queries are padded to for the tensor-core kernels
 
     # ---- what it wants
     def tensor_specs(self):
@@ -103,12 +107,21 @@ class Attention(Part):
         return specs
 
     def cache_need(self):
+        if self.room is not None:
+            return PagedKVNeed(self.kv_heads, self.room, self.window)
         return PagedKVNeed(self.kv_heads, self.dim, self.window, self.vdim if self.vdim != self.dim else None)
+
+    def _on_tensor_cores(self, dtype) -> bool:
+        """Whether the general path runs on the tensor-core kernels in a run of `dtype`."""
+        return (self.general and dtype == torch.bfloat16 and self.dim % 16 == 0 and self.vdim % 16 == 0
+                and self.q_heads // self.kv_heads <= 16)
 
     def parts(self):
         return [self.position] if self.position is not None else []
 
     def kernel_libraries(self, dtype):
+        if self._on_tensor_cores(dtype):
+            return ("elementwise", "attention_mma")
         if dtype == torch.float32 or self.general:
             return ("elementwise", "attention_simt")
         names = ["elementwise", "attention_mma"]
@@ -117,6 +130,8 @@ class Attention(Part):
         return tuple(names)
 
     def tile_sizes(self, dtype):
+        if self._on_tensor_cores(dtype):
+            return (ops.attention_mma_block_queries(),)
         if dtype == torch.float32 or self.general:
             return (ops.attention_simt_block_queries(),)
         sizes = [ops.attention_mma_block_queries()]
@@ -158,17 +173,30 @@ class Attention(Part):
         if self.qk_norm_eps is not None:
             self.q_norm_w, self.k_norm_w = tensors[n["q_norm"]], tensors[n["k_norm"]]
         self.sink = tensors[n["sink"]] if "sink" in n else None
+        if self._on_tensor_cores(runtime.dtype):
+            ops.attention_scratch(runtime.device)      # made now, never inside a graph capture
+            self.room = max(self.dim, self.vdim)
+            if self.room != self.vdim:                 # the heads' outputs arrive padded: zero columns in the output matrix
+                wide = torch.zeros((self.hidden, self.q_heads, self.room), dtype=self.w_o.dtype, device=self.w_o.device)
+                wide[:, :, : self.vdim] = self.w_o.view(self.hidden, self.q_heads, self.vdim)
+                self.w_o = wide.view(self.hidden, self.q_heads * self.room).contiguous()
 
     def _forward_general(self, h, batch, cache):
         tokens, group = h.shape[0], batch.groups[cache.group]
         proj = self.runtime.linear(h, self.w_qkv)
-        q = torch.empty((tokens, self.q_heads * self.dim), dtype=h.dtype, device=h.device)
+        room = self.room or self.dim
+        q = torch.empty((tokens, self.q_heads * room), dtype=h.dtype, device=h.device)
         gates = torch.empty((tokens, self.q_heads), dtype=torch.float32, device=h.device) if "gate" in self.names else None
         ops.qk_rownorm_kv(proj, q, cache.k_pool, cache.v_pool, self.q_norm_w, self.k_norm_w, group.slot_map, gates,
                           self.q_heads, self.kv_heads, self.dim, self.vdim, cache.page_tokens, float(self.qk_norm_eps or 0.0))
-        out = torch.empty((tokens, self.q_heads * self.vdim), dtype=h.dtype, device=h.device)
-        ops.attention_f32(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.dim, cache.page_tokens,
-                          self.scale, self.window or 0, self.vdim, self.sink, gates)
+        if self.room is not None:
+            out = torch.empty((tokens, self.q_heads * room), dtype=h.dtype, device=h.device)
+            ops.attention_bf16(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, room, cache.page_tokens,
+                               self.scale, self.window or 0, sinks=self.sink, gates=gates, exact_weights=True)
+        else:
+            out = torch.empty((tokens, self.q_heads * self.vdim), dtype=h.dtype, device=h.device)
+            ops.attention_f32(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.dim, cache.page_tokens,
+                              self.scale, self.window or 0, self.vdim, self.sink, gates)
         return self.runtime.linear(out, self.w_o)
 
     # ---- one step

@@ -264,13 +264,16 @@ def compare(rows, want, dtype):
         got = torch.from_numpy(np.stack([rows[rid][p] for p in range(reference.shape[0])])).to(F)
         bound = tolerance(reference.float(), dtype)
         if dtype == torch.bfloat16:
-            # eight layer runs of bfloat16 rounding leave a few outliers among thousands of logits: a row's
-            # root mean square error against half the bound, its largest error against twice the bound
-            worst = torch.maximum(2 * (got - reference).pow(2).mean(dim=1).sqrt(), (got - reference).abs().max(dim=1).values / 2)
+            # Norms after every sub-layer pass bfloat16's rounding on from layer run to layer run, so the bound
+            # is on a row's root mean square error, 1/16 of the row's own root mean square (a lost state, a
+            # window off by one or a missing sink changes a row by about its own size), and four times
+            # that for the row's largest error.
+            bound = reference.pow(2).mean(dim=1).sqrt() / 16
+            worst = torch.maximum((got - reference).pow(2).mean(dim=1).sqrt(), (got - reference).abs().max(dim=1).values / 4)
         else:
             worst = (got - reference).abs().max(dim=1).values
         bad = torch.nonzero(worst > bound)
-        assert bad.numel() == 0, f"{rid}: first wrong position {int(bad[0])} of {reference.shape[0]}, {worst[bad[0]].item():.3e} > {bound:.3e}"
+        assert bad.numel() == 0, f"{rid}: first wrong position {int(bad[0])} of {reference.shape[0]}, {worst[bad[0]].item():.3e}"
 
 
 CUTS = {"whole": whole, "tail": lambda r: tail_decoded(r, tail=40), "portions": portions, "mixed": mixed}
