@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights of a named Qwen3 shape.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--config 4b|4b-fp32|8b-mixed|32b-long]
+                    [--config 4b|4b-fp32|8b-mixed|32b-long|topidra]
 
 A step is one decode step. Every run prints ONE JSON line on standard output.
 
@@ -33,6 +33,11 @@ tokens (seeded), prompt portions of 2,048 tokens beside decoding requests, 512 n
 through `Engine`. --config 32b-long: the 32B shape, 8 prompts of 32,768 tokens, then 256 greedy
 decode steps.
 
+--config topidra: the Topidra design (linear-attention and sink-attention layers with norms around
+every sub-layer) beside Qwen3 at equal layer sizes, four layers each at three widths: prefill of
+2,048 tokens and decode at batch 8 for both, then Topidra's own kernels alone with the like kernel
+of the Qwen3 path beside each, as microseconds and fractions of the measured peaks.
+
 Peaks come from MEASURED_PEAKS.json beside this file when it exists (else 6.65 TB/s and
 1.59 PFLOP/s, an earlier measurement of the same kind of GPU). Inputs are synthetic token ids;
 weights are seeded random values of the named shape. Weights (8 GB and more) are larger than the
@@ -61,7 +66,7 @@ PROMPT, CONTEXT, PREFILL_TOKENS, PAGE = 2048, 4096, 2048, 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 FP32_TFLOPS = 75.0       # nominal FFMA rate of the part; only the 32-bit path's prefill fraction uses it
 CONFIGS = {"4b": ("qwen3-4b", "bf16"), "4b-fp32": ("qwen3-4b", "fp32"), "8b-mixed": ("qwen3-8b", "bf16"),
-           "32b-long": ("qwen3-32b", "bf16")}
+           "32b-long": ("qwen3-32b", "bf16"), "topidra": ("topidra", "bf16")}
 METRIC = "decode tokens/s (Qwen3-4B shape, batch 8, context 2048->4096)"
 
 
@@ -670,6 +675,170 @@ def run_32b_long(args, cfg, model, gen, pk, pk_source) -> dict:
     }
 
 
+# --------------------------------------------------------------------------------------- Topidra beside Qwen3
+TOPIDRA_SIZES = {   # name: (width, query heads, KV heads, head size, feed-forward width) of a Qwen3 family member
+    "0.6b-like": (1024, 16, 8, 128, 3072), "4b-like": (2560, 32, 8, 128, 9728), "8b-like": (4096, 32, 8, 128, 12288)}
+TOPIDRA_LAYERS, TOPIDRA_VOCAB, TOPIDRA_WINDOW = 4, 32768, 1024
+
+
+def topidra_pair(size: str):
+    """(Topidra configuration, Qwen3 configuration) of equal width, heads, feed-forward and depth: three
+    linear-attention layers and one sink-attention layer against four attention layers."""
+    import layover_b200 as lb
+
+    width, heads, kv, dim, ff = TOPIDRA_SIZES[size]
+    mlp = {"kind": "dense", "ff": ff}
+    linear = {"type": "lightning", "mlp": mlp, "mixer": {"heads": heads, "dim": dim, "vdim": dim,
+                                                         "decay": [1.0 - 2.0 ** -(3 + 6 * h / heads) for h in range(heads)]}}
+    softmax = {"type": "attention", "mlp": mlp, "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim,
+                                                          "scale": dim ** -0.5, "mask": {"size": TOPIDRA_WINDOW}}}
+    layers = tuple(softmax if i % 4 == 3 else linear for i in range(TOPIDRA_LAYERS))
+    topidra = lb.TopidraConfig(vocab=TOPIDRA_VOCAB, width=width, layers=layers)
+    qwen = lb.Qwen3Config(vocab_size=TOPIDRA_VOCAB, hidden_size=width, intermediate_size=ff, num_hidden_layers=TOPIDRA_LAYERS,
+                          num_attention_heads=heads, num_key_value_heads=kv, head_dim=dim, max_position_embeddings=40960,
+                          tie_word_embeddings=False)
+    return topidra, qwen
+
+
+def topidra_kernels(pk: dict) -> dict:
+    """Topidra's own kernels alone at the 4B-like layer size, each with the like kernel of the Qwen3
+    path: microseconds (kernels back to back in a replayed graph, operands rotating through more
+    memory than the L2 holds) and the fraction of the measured peak that bounds it."""
+    import torch
+    from layover_b200 import ops
+
+    width, heads, kv, dim, ff = TOPIDRA_SIZES["4b-like"]
+    dev, bf = "cuda", torch.bfloat16
+    hbm, tensor = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    out = {}
+
+    def point(name, fn, calls, nbytes=None, flops=None, peak_flops=None):
+        us = graph_time(fn, calls) * 1000.0
+        row = {"us": round(us, 2)}
+        if nbytes:
+            row["of_hbm"] = round(nbytes / (us * 1e-6) / hbm, 3)
+        if flops:
+            row["of_flops"] = round(flops / (us * 1e-6) / (peak_flops or tensor), 3)
+        out[name] = row
+
+    ROT = 6
+    for tokens in (2048, 8):
+        x = [torch.randn(tokens, width, device=dev) for _ in range(ROT)]
+        xb = [t.to(bf) for t in x]
+        delta = [torch.randn(tokens, width, device=dev, dtype=bf) for _ in range(ROT)]
+        w = torch.ones(width, device=dev)
+        o = torch.empty(tokens, width, device=dev, dtype=bf)
+        point(f"residual_rmsnorm_{tokens}", lambda i: ops.residual_rmsnorm(x[i % ROT], delta[i % ROT], w, 1e-6, None, w, 1e-6, o),
+              ROT, nbytes=tokens * width * (4 + 4 + 2 + 2))
+        point(f"like:add_rmsnorm_{tokens}", lambda i: ops.add_rmsnorm(xb[i % ROT], delta[i % ROT], w, 1e-6, o), ROT,
+              nbytes=tokens * width * (2 + 2 + 2 + 2))
+        gu = [torch.randn(tokens, 2 * ff, device=dev, dtype=bf) for _ in range(ROT)]
+        act = torch.empty(tokens, ff, device=dev, dtype=bf)
+        point(f"relu_gate_{tokens}", lambda i: ops.gated_act(gu[i % ROT], act, "relu", block=ops.SWIGLU_BLOCK), ROT,
+              nbytes=tokens * ff * 6)
+        point(f"like:swiglu_{tokens}", lambda i: ops.swiglu(gu[i % ROT], act, block=ops.SWIGLU_BLOCK), ROT, nbytes=tokens * ff * 6)
+
+    # ---- the linear-attention scan: a prompt portion (32-bit FMA bound) and single tokens (state traffic)
+    n = heads * dim
+    for tokens, seqs in ((2048, 1), (8, 8), (64, 64)):
+        proj = [torch.randn(tokens, 4 * n, device=dev, dtype=bf) for _ in range(ROT)]
+        state = torch.zeros(ROT, seqs + 1, heads, dim, dim, device=dev)
+        cu = torch.arange(0, tokens + 1, tokens // seqs, dtype=torch.int32, device=dev)
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        decay = torch.full((heads,), 0.99, device=dev)
+        scanned = torch.empty(tokens, n, device=dev)
+        gated = torch.empty(tokens, n, device=dev, dtype=bf)
+        wn = torch.ones(n, device=dev)
+        name = f"decay_scan_{'prompt2048' if seqs == 1 else f'decode_b{seqs}'}"
+        point(name, lambda i: ops.decay_scan(proj[i % ROT], 0, n, 2 * n, scanned, state[i % ROT], cu, slots, decay, seqs, heads,
+                                             dim, dim, "silu"), ROT,
+              nbytes=tokens * n * (3 * 2 + 4) + 2 * seqs * heads * dim * dim * 4,
+              flops=4.0 * tokens * heads * dim * dim, peak_flops=FP32_TFLOPS * 1e12)
+        point(f"gated_rmsnorm_{tokens}", lambda i: ops.gated_rmsnorm(scanned, proj[i % ROT][:, 3 * n:], wn, 1e-6, gated), ROT,
+              nbytes=tokens * n * (4 + 2 + 2))
+
+    # ---- sink attention beside the same kernels without sinks, gates and split weights
+    page = PAGE
+    for tokens, seqs, ctx in ((2048, 1, 2048), (8, 8, 3072), (64, 64, 3072)):
+        pages_per = -(-ctx // page)
+        pools = [torch.randn(2, seqs * pages_per + 1, kv, page, dim, device=dev, dtype=bf) for _ in range(ROT if seqs < 64 else 2)]
+        table = torch.arange(seqs * pages_per, dtype=torch.int32, device=dev).view(seqs, pages_per)
+        q = torch.randn(tokens, heads * dim, device=dev, dtype=bf)
+        o = torch.empty_like(q)
+        per = tokens // seqs
+        cu = torch.arange(0, tokens + 1, per, dtype=torch.int32, device=dev)
+        lens = torch.full((seqs,), ctx, dtype=torch.int32, device=dev)
+        sinks = torch.zeros(heads, device=dev)
+        gates = torch.rand(tokens, heads, device=dev)
+        seen = min(ctx, TOPIDRA_WINDOW)
+        R = len(pools)
+        if per > 1:
+            bq = ops.attention_mma_block_queries()
+            tq = torch.arange(0, per, bq, dtype=torch.int32, device=dev)
+            ts = torch.zeros_like(tq)
+            pairs = sum(min(p + 1, TOPIDRA_WINDOW) for p in range(per))
+            flops = 4.0 * heads * dim * pairs
+            for name, extra, factor in (("sink_attention_prompt2048", dict(sinks=sinks, gates=gates, exact_weights=True), 1.25),
+                                        ("like:attention_mma_prompt2048_window", {}, 1.0)):
+                point(name, lambda i: ops.attention_prefill_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu, lens, ts, tq,
+                                                                 tq.numel(), heads, kv, dim, page, dim ** -0.5, TOPIDRA_WINDOW,
+                                                                 **extra), R, flops=flops * factor)
+        else:
+            sms = ops.gemm_scratch(torch.device(dev))[2]
+            splits, stages = ops.decode_plan(seqs, heads, kv, dim, seen + 63, sms)
+            nbytes = seqs * kv * seen * 2 * dim * 2
+            for name, extra in ((f"sink_attention_decode_b{seqs}", dict(sinks=sinks, gates=gates, exact_weights=True)),
+                                (f"like:attention_decode_b{seqs}_window", {})):
+                point(name, lambda i: ops.attention_decode_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu, lens, None, seqs,
+                                                                heads, kv, dim, page, dim ** -0.5, TOPIDRA_WINDOW, splits, stages,
+                                                                **extra), R, nbytes=nbytes)
+        del pools
+        torch.cuda.empty_cache()
+    return out
+
+
+def step_bytes(model, batch: int, ctx: float) -> float:
+    """Bytes a decode step must move: every weight once; per request the keys and values a single token
+    can see (a window bounds them) and, for recurrent layers, the state read and written."""
+    import math
+    from layover_b200.parts.base import PagedKVNeed, StateNeed
+
+    element = 2 if str(model.dtype).endswith("bfloat16") else 4
+    per_request = 0.0
+    for _, need, reads in model.cache_needs():
+        if isinstance(need, PagedKVNeed):
+            per_request += need.elements_per_token() * element * (min(ctx, need.window) if need.window else ctx)
+        elif isinstance(need, StateNeed):
+            per_request += 2 * math.prod(need.shape) * 4
+    return model.weight_bytes() + batch * per_request
+
+
+def run_topidra(args, pk, pk_source) -> dict:
+    import torch
+    import layover_b200 as lb
+
+    gen = torch.Generator().manual_seed(0)
+    sizes = {}
+    for size in TOPIDRA_SIZES:
+        row = {}
+        for name, cfg in zip(("topidra", "qwen3"), topidra_pair(size)):
+            model = lb.random_model(cfg, seed=0, device="cuda", dtype=args.dtype, std=0.02)
+            prefill = prefill_point(model, gen, repeats=5)
+            decode = decode_point(model, args.batch, min(args.steps, 64), args.warmup, gen)
+            row[name] = {"prefill_tok_s": round(prefill["tok_s"], 1), "prefill_ms": round(prefill["ms"], 3),
+                         "decode_tok_s": round(decode["tok_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                         "decode_of_hbm": round(step_bytes(model, args.batch, decode["mean_ctx"])
+                                                / (decode["ms_per_step"] * 1e-3) / (pk["hbm_gbs"] * 1e9), 3),
+                         "launches_per_step": round(decode["launches"] / min(args.steps, 64), 1)}
+            del model
+            torch.cuda.empty_cache()
+        sizes[size] = row
+    return {"metric": "Topidra beside Qwen3 at equal layer sizes: prefill of 2,048 tokens and decode at batch "
+                      f"{args.batch}, {TOPIDRA_LAYERS} layers, vocabulary {TOPIDRA_VOCAB}",
+            "dtype": args.dtype, "data": "synthetic token ids, seeded random weights", "peaks": pk_source,
+            "window": TOPIDRA_WINDOW, "sizes": sizes, "kernels": topidra_kernels(pk)}
+
+
 def lb_preset(name: str):
     import layover_b200 as lb
     return lb.preset(name)
@@ -686,6 +855,8 @@ def run_ours(args) -> dict:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
     pk, pk_source = peaks()
+    if args.config == "topidra":
+        return run_topidra(args, pk, pk_source)
     if args.only == "kernels":
         return {"only": "kernels", **kernel_points(args.model, pk, with_library=True)}
     if args.only == "plans":
@@ -831,7 +1002,8 @@ def main(argv=None) -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--config", default="4b", choices=sorted(CONFIGS),
                         help="4b: the headline; 4b-fp32: the 32-bit path; 8b-mixed: 32 mixed requests through the "
-                             "scheduler; 32b-long: 8 x 32,768-token contexts")
+                             "scheduler; 32b-long: 8 x 32,768-token contexts; topidra: the Topidra design beside "
+                             "Qwen3 at equal layer sizes, and its kernels alone")
     parser.add_argument("--model", default=None, help="a preset's name instead of the one --config names")
     parser.add_argument("--dtype", default=None, choices=["bf16", "fp32"])
     parser.add_argument("--batch", type=int, default=8)

@@ -539,7 +539,29 @@ LB_EXPORT int lb_gated_act(int dtype, const void* gate_up, void* out, int tokens
 //   out[r] = T(weight * v * rsqrt(mean(v^2) + eps))    (weight null: no output, only the sum)
 // Everything is computed in 32-bit and rounded once, at the store of out. One block per row; the
 // block size depends on the width only, so a row's sums do not depend on the batch.
-template <typename T>
+// four neighbouring elements with one access (8 bytes of bf16, 16 of float)
+template <typename T> struct Four;
+template <> struct Four<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Four<bf16> {
+  static __device__ __forceinline__ float4 load(const bf16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x), b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  }
+  static __device__ __forceinline__ void store(bf16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<const uint32_t*>(&a);
+    r.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+  }
+};
+
+// VEC: the width is a multiple of 4 and every row starts on a 16-byte (8-byte for bf16) boundary.
+template <typename T, bool VEC>
 __global__ void residual_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
                                         const float* __restrict__ delta_w, float delta_eps,
                                         const float* __restrict__ extra, const float* __restrict__ weight,
@@ -555,27 +577,63 @@ __global__ void residual_rmsnorm_kernel(float* __restrict__ x, const T* __restri
   float dinv = 1.f;
   if (dr && delta_w) {
     float ds = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-      const float d = Elem<T>::load(dr + i);
-      ds += d * d;
+    if (VEC) {
+      for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+        const float4 d = Four<T>::load(dr + i);
+        ds += d.x * d.x + d.y * d.y + d.z * d.z + d.w * d.w;
+      }
+    } else {
+      for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float d = Elem<T>::load(dr + i);
+        ds += d * d;
+      }
     }
     ds = block_sum(ds, scratch);
     dinv = 1.0f / sqrtf(ds / (float)hidden + delta_eps);
   }
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = xr[i];
-    if (dr) v += delta_w ? Elem<T>::load(dr + i) * dinv * delta_w[i] : Elem<T>::load(dr + i);
-    if (er) v += er[i];
-    if (!rows && (dr || er)) xr[i] = v;
-    row_vals[i] = v;
-    ss += v * v;
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      float4 v = Four<float>::load(xr + i);
+      if (dr) {
+        const float4 d = Four<T>::load(dr + i);
+        if (delta_w) {
+          const float4 w = Four<float>::load(delta_w + i);
+          v.x += d.x * dinv * w.x; v.y += d.y * dinv * w.y; v.z += d.z * dinv * w.z; v.w += d.w * dinv * w.w;
+        } else {
+          v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        }
+      }
+      if (er) {
+        const float4 e = Four<float>::load(er + i);
+        v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w;
+      }
+      if (!rows && (dr || er)) Four<float>::store(xr + i, v);
+      Four<float>::store(row_vals + i, v);
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = xr[i];
+      if (dr) v += delta_w ? Elem<T>::load(dr + i) * dinv * delta_w[i] : Elem<T>::load(dr + i);
+      if (er) v += er[i];
+      if (!rows && (dr || er)) xr[i] = v;
+      row_vals[i] = v;
+      ss += v * v;
+    }
   }
   if (!weight) return;
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
   T* o = out + (size_t)blockIdx.x * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) Elem<T>::store(o + i, weight[i] * (row_vals[i] * inv));
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      const float4 v = Four<float>::load(row_vals + i), w = Four<float>::load(weight + i);
+      Four<T>::store(o + i, make_float4(w.x * (v.x * inv), w.y * (v.y * inv), w.z * (v.z * inv), w.w * (v.w * inv)));
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) Elem<T>::store(o + i, weight[i] * (row_vals[i] * inv));
+  }
 }
 
 template <typename T>
@@ -585,11 +643,20 @@ static int launch_residual_rmsnorm(float* x, const void* delta, const float* del
   static LbPerDeviceOnce once;
   const size_t smem = (size_t)(hidden + 33) * sizeof(float);
   if (smem > 200 * 1024) return LB_ERR_SIZE;
-  if (smem > 48 * 1024 && once.first())
-    cudaFuncSetAttribute(residual_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-  lb_launch(residual_rmsnorm_kernel<T>, n_rows, threads, smem, stream, x, (const T*)delta, delta_w, delta_eps, extra, weight,
-            (T*)out, rows, hidden, eps);
+  if (smem > 48 * 1024 && once.first()) {
+    cudaFuncSetAttribute(residual_rmsnorm_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(residual_rmsnorm_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  }
+  // the form, like the block size, depends on the width and the buffers' alignment only, never on the batch
+  const bool vec = hidden % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)extra % 16 == 0 &&
+                   (uintptr_t)out % 16 == 0 && (uintptr_t)delta_w % 16 == 0 && (uintptr_t)weight % 16 == 0;
+  const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+  if (vec)
+    lb_launch(residual_rmsnorm_kernel<T, true>, n_rows, threads, smem, stream, x, (const T*)delta, delta_w, delta_eps, extra,
+              weight, (T*)out, rows, hidden, eps);
+  else
+    lb_launch(residual_rmsnorm_kernel<T, false>, n_rows, threads, smem, stream, x, (const T*)delta, delta_w, delta_eps, extra,
+              weight, (T*)out, rows, hidden, eps);
   return lb_last_error();
 }
 

@@ -14,34 +14,39 @@
 // depend on how the tokens were cut into steps or on what else is in the batch, bit for bit.
 // State, decay, products and sums are 32-bit; only q, k, v arrive in the run's type T.
 //
-// Grid (ceil(vdim / 32), heads, sequences), 256 threads: warp r owns rows [r * DPT, (r + 1) * DPT)
-// of S, lane j column blockIdx.x * 32 + j, so a thread keeps DPT state elements in registers and
-// never synchronises inside a token. Tokens are taken CHUNK at a time: q, k, v of the chunk go to
-// shared memory (k and q are read as broadcasts), each warp leaves its partial sums of o per token,
-// and the eight partial sums are added in warp order at the end of the chunk.
+// Grid (ceil(vdim / 32), heads, sequences), RANGES warps: warp r owns rows [r * DPT, (r + 1) * DPT) of
+// S, lane j column blockIdx.x * 32 + j, so a thread keeps DPT state elements in registers and never
+// synchronises inside a token. Tokens are taken CHUNK (8) at a time through two buffers in shared
+// memory: while a chunk is computed (k and q are read as 16-byte broadcasts, each warp leaves its
+// partial sums of o per token), the next chunk's q, k, v are already on their way from global
+// memory into registers; the warps' partial sums are added in warp order at the end of the chunk.
+// RANGES and DPT depend on the head size only, never on the batch.
 #include <math.h>
 
 #include "common.cuh"
 
 namespace {
-constexpr int RANGES = 8;     // warps: ranges of state rows
 constexpr int COLS = 32;      // value columns per block (one per lane)
+constexpr int CHUNK = 8;      // tokens per trip through shared memory (a thread stages at most one value of v: CHUNK * 32 <= threads)
 
 template <int ACT> __device__ __forceinline__ float activate(float z) {
-  return ACT == 1 ? z / (1.0f + expf(-z)) : z;      // 1: silu, 0: none
+  return ACT == 1 ? z / (1.0f + __expf(-z)) : z;      // 1: silu, 0: none
 }
 
-template <typename T, int DPT, int ACT>
+template <typename T, int RANGES, int DPT, int ACT>
 __global__ void __launch_bounds__(RANGES * COLS)
 decay_scan_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_off, int v_off,
                   float* __restrict__ out, float* __restrict__ state, const int* __restrict__ cu_q,
                   const int* __restrict__ state_slots, const float* __restrict__ decay, int heads, int dim, int vdim) {
-  constexpr int DPAD = RANGES * DPT;
-  constexpr int CHUNK = DPT >= 32 ? 8 : 16;     // tokens per trip through shared memory (under 48 KB in all)
-  __shared__ __align__(16) float q_s[CHUNK][DPAD];
-  __shared__ __align__(16) float k_s[CHUNK][DPAD];
-  __shared__ float v_s[CHUNK][COLS];
-  __shared__ float part_s[CHUNK][RANGES][COLS];
+  static_assert(DPT % 4 == 0, "16-byte broadcasts");
+  static_assert(CHUNK * COLS <= RANGES * COLS, "one value of v per staging thread");
+  constexpr int DPAD = RANGES * DPT, THREADS = RANGES * COLS;
+  constexpr int QK_EACH = (CHUNK * DPAD + THREADS - 1) / THREADS;     // q (and k) elements a thread stages per chunk
+  extern __shared__ __align__(16) float scan_smem[];
+  float (*q_s)[CHUNK][DPAD] = reinterpret_cast<float (*)[CHUNK][DPAD]>(scan_smem);                       // [2][CHUNK][DPAD]
+  float (*k_s)[CHUNK][DPAD] = reinterpret_cast<float (*)[CHUNK][DPAD]>(scan_smem + 2 * CHUNK * DPAD);    // [2][CHUNK][DPAD]
+  float (*v_s)[CHUNK][COLS] = reinterpret_cast<float (*)[CHUNK][COLS]>(scan_smem + 4 * CHUNK * DPAD);    // [2][CHUNK][COLS]
+  float (*part_s)[RANGES][COLS] = reinterpret_cast<float (*)[RANGES][COLS]>(scan_smem + 4 * CHUNK * DPAD + 2 * CHUNK * COLS);
   pdl_launch_dependents();
   pdl_wait();
   const int seq = blockIdx.z, head = blockIdx.y, e0 = blockIdx.x * COLS;
@@ -55,35 +60,66 @@ decay_scan_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_
     const int d = r * DPT + x;
     s[x] = (d < dim && e < vdim) ? mine[(size_t)d * vdim + e] : 0.f;
   }
-  for (int t0 = 0; t0 < count; t0 += CHUNK) {
-    const int n = min(CHUNK, count - t0);
-    __syncthreads();                         // the partial sums of the chunk before have been read
-    for (int i = threadIdx.x; i < n * DPAD; i += blockDim.x) {
-      const int t = i / DPAD, d = i - t * DPAD;
-      const T* row = proj + (size_t)(first + t0 + t) * row_stride;
-      q_s[t][d] = d < dim ? activate<ACT>(Elem<T>::load(row + q_off + head * dim + d)) : 0.f;
-      k_s[t][d] = d < dim ? activate<ACT>(Elem<T>::load(row + k_off + head * dim + d)) : 0.f;
-    }
-    for (int i = threadIdx.x; i < n * COLS; i += blockDim.x) {
-      const int t = i / COLS, c = i - t * COLS;
-      const T* row = proj + (size_t)(first + t0 + t) * row_stride;
-      v_s[t][c] = e0 + c < vdim ? activate<ACT>(Elem<T>::load(row + v_off + head * vdim + e0 + c)) : 0.f;
-    }
-    __syncthreads();
-    for (int t = 0; t < n; ++t) {
-      const float v = v_s[t][j];
-      const float* kr = &k_s[t][r * DPT];
-      const float* qr = &q_s[t][r * DPT];
-      float partial = 0.f;
+  // what this thread fetches of a chunk: QK_EACH elements of q and of k, and (the first CHUNK * 32 threads) one of v
+  float q_reg[QK_EACH], k_reg[QK_EACH], v_reg = 0.f;
+  auto fetch = [&](int t0, int n) {
 #pragma unroll
-      for (int x = 0; x < DPT; ++x) {
-        s[x] = fmaf(kr[x], v, lam * s[x]);
-        partial = fmaf(s[x], qr[x], partial);
+    for (int u = 0; u < QK_EACH; ++u) {
+      const int i = threadIdx.x + u * THREADS, t = i / DPAD, d = i - t * DPAD;
+      q_reg[u] = k_reg[u] = 0.f;
+      if (t < n && d < dim) {
+        const T* row = proj + (size_t)(first + t0 + t) * row_stride + head * dim + d;
+        q_reg[u] = Elem<T>::load(row + q_off);
+        k_reg[u] = Elem<T>::load(row + k_off);
       }
-      part_s[t][r][j] = partial;
+    }
+    if (threadIdx.x < CHUNK * COLS) {
+      const int t = threadIdx.x / COLS, c = threadIdx.x - t * COLS;
+      v_reg = (t < n && e0 + c < vdim)
+                  ? Elem<T>::load(proj + (size_t)(first + t0 + t) * row_stride + v_off + head * vdim + e0 + c) : 0.f;
+    }
+  };
+  auto stage = [&](int buf) {
+#pragma unroll
+    for (int u = 0; u < QK_EACH; ++u) {
+      const int i = threadIdx.x + u * THREADS, t = i / DPAD, d = i - t * DPAD;
+      if (t < CHUNK) {
+        q_s[buf][t][d] = activate<ACT>(q_reg[u]);
+        k_s[buf][t][d] = activate<ACT>(k_reg[u]);
+      }
+    }
+    if (threadIdx.x < CHUNK * COLS) v_s[buf][threadIdx.x / COLS][threadIdx.x % COLS] = activate<ACT>(v_reg);
+  };
+  fetch(0, min(CHUNK, count));
+  stage(0);
+  __syncthreads();
+  int buf = 0;
+  for (int t0 = 0; t0 < count; t0 += CHUNK, buf ^= 1) {
+    const int n = min(CHUNK, count - t0);
+    const bool more = t0 + CHUNK < count;
+    if (more) fetch(t0 + CHUNK, min(CHUNK, count - t0 - CHUNK));     // in flight while this chunk is computed
+#pragma unroll 2
+    for (int t = 0; t < n; ++t) {
+      const float v = v_s[buf][t][j];
+      const float4* kr = reinterpret_cast<const float4*>(&k_s[buf][t][r * DPT]);
+      const float4* qr = reinterpret_cast<const float4*>(&q_s[buf][t][r * DPT]);
+      float partial[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int x4 = 0; x4 < DPT / 4; ++x4) {
+        const float4 k4 = kr[x4], q4 = qr[x4];
+        s[4 * x4 + 0] = fmaf(k4.x, v, lam * s[4 * x4 + 0]);
+        s[4 * x4 + 1] = fmaf(k4.y, v, lam * s[4 * x4 + 1]);
+        s[4 * x4 + 2] = fmaf(k4.z, v, lam * s[4 * x4 + 2]);
+        s[4 * x4 + 3] = fmaf(k4.w, v, lam * s[4 * x4 + 3]);
+        partial[0] = fmaf(s[4 * x4 + 0], q4.x, partial[0]);
+        partial[1] = fmaf(s[4 * x4 + 1], q4.y, partial[1]);
+        partial[2] = fmaf(s[4 * x4 + 2], q4.z, partial[2]);
+        partial[3] = fmaf(s[4 * x4 + 3], q4.w, partial[3]);
+      }
+      part_s[t][r][j] = (partial[0] + partial[1]) + (partial[2] + partial[3]);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < n * COLS; i += blockDim.x) {
+    for (int i = threadIdx.x; i < n * COLS; i += THREADS) {
       const int t = i / COLS, c = i - t * COLS;
       if (e0 + c >= vdim) continue;
       float total = 0.f;
@@ -91,6 +127,8 @@ decay_scan_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_
       for (int w = 0; w < RANGES; ++w) total += part_s[t][w][c];
       out[((size_t)(first + t0 + t) * heads + head) * vdim + e0 + c] = total;
     }
+    if (more) stage(buf ^ 1);
+    __syncthreads();      // the partial sums have been read, the next chunk is in place
   }
 #pragma unroll
   for (int x = 0; x < DPT; ++x) {
@@ -99,16 +137,23 @@ decay_scan_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_
   }
 }
 
-template <typename T, int DPT>
+template <typename T, int RANGES, int DPT>
 int launch_scan(int act, dim3 grid, cudaStream_t stream, const void* proj, long row_stride, int q_off, int k_off, int v_off,
                 float* out, float* state, const int* cu_q, const int* state_slots, const float* decay, int heads,
                 int dim, int vdim) {
+  // q and k twice (two buffers), v twice, the warps' partial sums
+  constexpr size_t smem = (size_t)(4 * CHUNK * RANGES * DPT + 2 * CHUNK * COLS + CHUNK * RANGES * COLS) * sizeof(float);
+  static LbPerDeviceOnce once;
+  if (smem > 48 * 1024 && once.first()) {
+    cudaFuncSetAttribute(decay_scan_kernel<T, RANGES, DPT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(decay_scan_kernel<T, RANGES, DPT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
   if (act == 1)
-    lb_launch(decay_scan_kernel<T, DPT, 1>, grid, RANGES * COLS, 0, stream, (const T*)proj, row_stride, q_off, k_off, v_off,
-              out, state, cu_q, state_slots, decay, heads, dim, vdim);
+    lb_launch(decay_scan_kernel<T, RANGES, DPT, 1>, grid, RANGES * COLS, smem, stream, (const T*)proj, row_stride, q_off, k_off,
+              v_off, out, state, cu_q, state_slots, decay, heads, dim, vdim);
   else
-    lb_launch(decay_scan_kernel<T, DPT, 0>, grid, RANGES * COLS, 0, stream, (const T*)proj, row_stride, q_off, k_off, v_off,
-              out, state, cu_q, state_slots, decay, heads, dim, vdim);
+    lb_launch(decay_scan_kernel<T, RANGES, DPT, 0>, grid, RANGES * COLS, smem, stream, (const T*)proj, row_stride, q_off, k_off,
+              v_off, out, state, cu_q, state_slots, decay, heads, dim, vdim);
   return lb_last_error();
 }
 
@@ -116,18 +161,18 @@ template <typename T>
 int dispatch_scan(int act, dim3 grid, cudaStream_t stream, const void* proj, long row_stride, int q_off, int k_off,
                   int v_off, float* out, float* state, const int* cu_q, const int* state_slots, const float* decay,
                   int heads, int dim, int vdim) {
-#define LB_SCAN(D) launch_scan<T, D>(act, grid, stream, proj, row_stride, q_off, k_off, v_off, out, state, cu_q, state_slots, \
-                                     decay, heads, dim, vdim)
-  if (dim <= RANGES * 4) return LB_SCAN(4);
-  if (dim <= RANGES * 8) return LB_SCAN(8);
-  if (dim <= RANGES * 16) return LB_SCAN(16);
-  return LB_SCAN(32);
+#define LB_SCAN(R, D) launch_scan<T, R, D>(act, grid, stream, proj, row_stride, q_off, k_off, v_off, out, state, cu_q, \
+                                           state_slots, decay, heads, dim, vdim)
+  if (dim <= 32) return LB_SCAN(8, 4);          // the split of S over warps is a function of the head size alone
+  if (dim <= 64) return LB_SCAN(16, 4);
+  if (dim <= 128) return LB_SCAN(16, 8);
+  return LB_SCAN(8, 32);
 #undef LB_SCAN
 }
 
 // out[t, i] = T(x[t, i] * rsqrt(mean_i x[t, i]^2 + eps) * weight[i] / (1 + exp(-gate[t, i])))
 // x 32-bit [tokens, n]; gate logits in the run's type inside a wider row (gate_stride elements apart).
-template <typename T>
+template <typename T, bool VEC>
 __global__ void gated_rmsnorm_kernel(const float* __restrict__ x, const T* __restrict__ gate, long gate_stride,
                                      const float* __restrict__ weight, T* __restrict__ out, int n, float eps) {
   __shared__ float scratch[33];
@@ -135,12 +180,30 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ x, const T* __res
   pdl_wait();
   const float* xr = x + (size_t)blockIdx.x * n;
   const T* gr = gate + (size_t)blockIdx.x * gate_stride;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];
-  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
   T* o = out + (size_t)blockIdx.x * n;
-  for (int i = threadIdx.x; i < n; i += blockDim.x)
-    Elem<T>::store(o + i, xr[i] * inv * weight[i] / (1.0f + expf(-Elem<T>::load(gr + i))));
+  float ss = 0.f;
+  if (VEC) {        // n a multiple of 4, rows on 16-byte (bf16: 8-byte) boundaries
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(xr + i);
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(xr + i), w = *reinterpret_cast<const float4*>(weight + i);
+      float g[4], y[4] = {v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) g[u] = Elem<T>::load(gr + i + u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) Elem<T>::store(o + i + u, y[u] / (1.0f + expf(-g[u])));
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+      Elem<T>::store(o + i, xr[i] * inv * weight[i] / (1.0f + expf(-Elem<T>::load(gr + i))));
+  }
 }
 }  // namespace
 
@@ -150,7 +213,7 @@ LB_EXPORT int lb_decay_scan(int dtype, const void* proj, long row_stride, int q_
                             float* state, const int* cu_q, const int* state_slots, const float* decay, int n_seqs,
                             int heads, int dim, int vdim, int act, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
-  if (heads <= 0 || heads > 65535 || n_seqs > 65535 || dim <= 0 || dim > RANGES * 32 || vdim <= 0 || act < 0 || act > 1)
+  if (heads <= 0 || heads > 65535 || n_seqs > 65535 || dim <= 0 || dim > 256 || vdim <= 0 || act < 0 || act > 1)
     return LB_ERR_SIZE;
   const dim3 grid((vdim + COLS - 1) / COLS, heads, n_seqs);
   if (dtype == LB_F32)
@@ -167,13 +230,14 @@ LB_EXPORT int lb_gated_rmsnorm(int dtype, const float* x, const void* gate, long
   if (tokens <= 0) return 0;
   if (n <= 0) return LB_ERR_SIZE;
   const int threads = n >= 1024 ? 256 : 128;
-  if (dtype == LB_F32)
-    lb_launch(gated_rmsnorm_kernel<float>, tokens, threads, 0, stream, x, (const float*)gate, gate_stride, weight,
-              (float*)out, n, eps);
-  else if (dtype == LB_BF16)
-    lb_launch(gated_rmsnorm_kernel<bf16>, tokens, threads, 0, stream, x, (const bf16*)gate, gate_stride, weight,
-              (bf16*)out, n, eps);
-  else
+  const bool vec = n % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)weight % 16 == 0;
+  if (dtype == LB_F32) {
+    if (vec) lb_launch(gated_rmsnorm_kernel<float, true>, tokens, threads, 0, stream, x, (const float*)gate, gate_stride, weight, (float*)out, n, eps);
+    else lb_launch(gated_rmsnorm_kernel<float, false>, tokens, threads, 0, stream, x, (const float*)gate, gate_stride, weight, (float*)out, n, eps);
+  } else if (dtype == LB_BF16) {
+    if (vec) lb_launch(gated_rmsnorm_kernel<bf16, true>, tokens, threads, 0, stream, x, (const bf16*)gate, gate_stride, weight, (bf16*)out, n, eps);
+    else lb_launch(gated_rmsnorm_kernel<bf16, false>, tokens, threads, 0, stream, x, (const bf16*)gate, gate_stride, weight, (bf16*)out, n, eps);
+  } else
     return LB_ERR_DTYPE;
   return lb_last_error();
 }
