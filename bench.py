@@ -750,8 +750,14 @@ def topidra_kernels(pk: dict) -> dict:
         gated = torch.empty(tokens, n, device=dev, dtype=bf)
         wn = torch.ones(n, device=dev)
         name = f"decay_scan_{'prompt2048' if seqs == 1 else f'decode_b{seqs}'}"
+        seg_tokens, segments = ops.scan_segments([tokens // seqs] * seqs, 4 * heads * dim * dim)     # as the mixer runs it
+        scratch = torch.empty(segments, heads, dim, dim, device=dev) if segments else None
+        if segments:
+            point(name + "_single_pass", lambda i: ops.decay_scan(proj[i % ROT], 0, n, 2 * n, scanned, state[i % ROT], cu, slots,
+                                                                  decay, seqs, heads, dim, dim, "silu"), ROT,
+                  flops=4.0 * tokens * heads * dim * dim, peak_flops=FP32_TFLOPS * 1e12)
         point(name, lambda i: ops.decay_scan(proj[i % ROT], 0, n, 2 * n, scanned, state[i % ROT], cu, slots, decay, seqs, heads,
-                                             dim, dim, "silu"), ROT,
+                                             dim, dim, "silu", seg_tokens, scratch), ROT,
               nbytes=tokens * n * (3 * 2 + 4) + 2 * seqs * heads * dim * dim * 4,
               flops=4.0 * tokens * heads * dim * dim, peak_flops=FP32_TFLOPS * 1e12)
         point(f"gated_rmsnorm_{tokens}", lambda i: ops.gated_rmsnorm(scanned, proj[i % ROT][:, 3 * n:], wn, 1e-6, gated), ROT,

@@ -278,14 +278,26 @@ SCAN_ACTIVATIONS = {None: 0, "none": 0, "silu": 1}
 
 def decay_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torch.Tensor, state: torch.Tensor,
                cu_q: torch.Tensor, state_slots: torch.Tensor, decay: torch.Tensor, n_seqs: int, heads: int, dim: int,
-               vdim: int, activation: str | None = None) -> torch.Tensor:
+               vdim: int, activation: str | None = None, segment_tokens: int = 0,
+               segment_state: torch.Tensor | None = None) -> torch.Tensor:
     """Per sequence and head S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over the step's tokens, from and
     to the requests' state slots.
 
     proj [T, N] holds q at column q_off (heads*dim), k at k_off, v at v_off (heads*vdim), each passed through
     `activation` on the way in; out float32 [T, heads*vdim]; state float32 [slots, heads, dim, vdim];
-    decay float32 [heads]; cu_q int32 [S + 1]; state_slots int32 [S]."""
+    decay float32 [heads]; cu_q int32 [S + 1]; state_slots int32 [S].
+
+    With `segment_tokens` > 0 every sequence's tokens are cut into segments of that many that are scanned at once
+    (three launches; for steps with long portions, where one chain per sequence and head would leave most of
+    the device idle): `segment_state` is float32 scratch [sum over sequences of max(1, ceil(tokens / segment_tokens)),
+    heads, dim, vdim] (`scan_segments` counts them). The result agrees with the single pass within rounding."""
     _need(out, torch.float32, "out"); _need(state, torch.float32, "state"); _need(decay, torch.float32, "decay")
+    total_segments = 0
+    if segment_tokens:
+        _need(segment_state, torch.float32, "segment_state")
+        total_segments = segment_state.shape[0]
+        if tuple(segment_state.shape[1:]) != (heads, dim, vdim) or total_segments < n_seqs:
+            raise ValueError("decay_scan: segment_state must be [segments, heads, dim, vdim] with a segment or more per sequence")
     _need(cu_q, torch.int32, "cu_q"); _need(state_slots, torch.int32, "state_slots")
     tokens = proj.shape[0]
     if proj.dim() != 2 or proj.stride(1) != 1 or max(q_off, k_off) + heads * dim > proj.shape[1] \
@@ -296,11 +308,32 @@ def decay_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torc
     if activation not in SCAN_ACTIVATIONS:
         raise ValueError(f"decay_scan: unknown activation {activation!r}")
     fn = _fn("linear_attention", "lb_decay_scan",
-             [c_int, c_void_p, c_long, c_int, c_int, c_int] + [c_void_p] * 5 + [c_int] * 5 + [c_void_p])
+             [c_int, c_void_p, c_long, c_int, c_int, c_int] + [c_void_p] * 5 + [c_int] * 5 + [c_void_p, c_int, c_int, c_void_p])
     _check(fn(dtype_code(proj.dtype), _ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(out), _ptr(state), _ptr(cu_q),
-              _ptr(state_slots), _ptr(decay), n_seqs, heads, dim, vdim, SCAN_ACTIVATIONS[activation], _stream()),
-           "decay_scan")
+              _ptr(state_slots), _ptr(decay), n_seqs, heads, dim, vdim, SCAN_ACTIVATIONS[activation],
+              _ptr(segment_state), int(segment_tokens), total_segments, _stream()), "decay_scan")
+    if total_segments:
+        global LAUNCHES
+        LAUNCHES += 2          # the segmented form is three kernels
     return out
+
+
+SCAN_SEGMENT_TOKENS = 128      # the shortest segment of the segmented scan
+SCAN_SEGMENT_BYTES = 1 << 30   # the most scratch its segments' states may take; longer segments beyond
+
+
+def scan_segments(q_lens: list[int], state_bytes: int) -> tuple[int, int]:
+    """(tokens per segment, number of segments) for a step whose sequences bring `q_lens` tokens, or (0, 0)
+    when no portion is long enough for the segmented scan to pay (two segments or more)."""
+    longest = max(q_lens)
+    if longest < 2 * SCAN_SEGMENT_TOKENS:
+        return 0, 0
+    tokens = SCAN_SEGMENT_TOKENS
+    while True:
+        total = sum(max(1, -(-n // tokens)) for n in q_lens)
+        if total * state_bytes <= SCAN_SEGMENT_BYTES or 2 * tokens > longest:
+            return tokens, total
+        tokens *= 2
 
 
 def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:

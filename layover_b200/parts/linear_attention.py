@@ -25,9 +25,12 @@ class DecayLinearAttention(Part):
     params: hidden, heads, head_dim, v_head_dim, decay (one number, or one per head), norm_eps,
     activation ("silu" or None); tensor names q, k, v, gate, o, norm relative to the prefix.
 
-    One kernel walks a sequence's tokens of the step in order, whether they are a prompt, a portion
-    or a single token, so the result does not depend on the cut. The four projections are stacked
-    at load into one matrix and read from the product's rows in place."""
+    One kernel walks a sequence's tokens of the step in order, whether they are a portion or a
+    single token, so the result does not depend on the cut. A step that holds a long portion (256
+    tokens and more of one request) cuts every portion into segments that are scanned at once and
+    joined by the state that comes into each (`ops.scan_segments`): the same sums in another
+    order, equal within rounding. The four projections are stacked at load into one matrix and
+    read from the product's rows in place."""
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -74,8 +77,10 @@ class DecayLinearAttention(Part):
         tokens, qk, vv = h.shape[0], self.heads * self.dim, self.heads * self.vdim
         proj = self.runtime.linear(h, self.w_in)                    # [T, q | k | v | gate (| padding)]
         scanned = torch.empty((tokens, vv), dtype=torch.float32, device=h.device)
+        segment_tokens, segments = ops.scan_segments(batch.q_lens, 4 * self.heads * self.dim * self.vdim)
+        scratch = torch.empty((segments, self.heads, self.dim, self.vdim), dtype=torch.float32, device=h.device) if segments else None
         ops.decay_scan(proj, 0, qk, 2 * qk, scanned, cache.state, batch.cu_q, batch.state_slots, self.decay, batch.n_seqs,
-                       self.heads, self.dim, self.vdim, self.activation)
+                       self.heads, self.dim, self.vdim, self.activation, segment_tokens, scratch)
         gated = torch.empty((tokens, vv), dtype=h.dtype, device=h.device)
         ops.gated_rmsnorm(scanned, proj[:, 2 * qk + vv: 2 * qk + 2 * vv], self.norm_w, self.norm_eps, gated)
         return self.runtime.linear(gated, self.w_o)

@@ -219,15 +219,13 @@ def test_decay_scan_carries_its_state_across_any_cut(dtype, heads, d, e, decay):
     got_a.append(step([(a, rows[at:])])[0])
     close(torch.cat(got_a)[:, : heads * e], want, dtype, "beside another")
     close(torch.cat(got_b)[:, : heads * e], want_other, dtype, "the other")
-    if dtype == torch.float32:        # the recurrence takes the same steps whatever the cut: the same bits
-        assert torch.equal(torch.cat(got_a), run_cuts_keep(cache, step, rows))
-
-
-def run_cuts_keep(cache, step, rows):
-    seq = cache.open("whole-again")
-    out = step([(seq, rows)])[0]
-    cache.close(seq)
-    return out
+    if dtype == torch.float32:
+        # portions too short for the segmented form take the same steps whatever the cut: the same bits
+        again = run_cuts(cache, step, rows, [100, 1, 99, 2, 98])
+        assert torch.equal(torch.cat(got_a), again)
+        # a whole prompt is cut into segments that run at once: the same sums in another order
+        assert ops.scan_segments([n], 4)[1] > 1
+        close(run_cuts(cache, step, rows, [n]), again.to(F), torch.float32, "segmented")
 
 
 # ------------------------------------------------------------------ whole models
@@ -243,7 +241,7 @@ def folders(tmp_path_factory):
     return out
 
 
-LENGTHS = [1, 9, 70, 130, 33, 97]
+LENGTHS = [1, 9, 70, 130, 33, 300]      # the longest is long enough for the segmented scan when it comes whole
 _expected = {}
 
 
@@ -341,3 +339,42 @@ def test_greedy_generation_through_the_engine(folders, name, graphs):
             if top[0] - top[1] > 1e-3 * logits.abs().max():     # a near tie may fall either way
                 assert token == int(logits.argmax()), f"position {len(sequence)}"
             sequence.append(token)
+
+
+def test_command_line_and_the_replay_program(folders, tmp_path):
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+
+    folder, raw, weights = folders["mid_loop"]
+    prompts = ([5, 17, 3, 44, 2, 9, 130], [9])
+    out = subprocess.run([sys.executable, "-m", "layover_b200", "--model", str(folder), "--dtype", "fp32",
+                          "--prompt-ids", ",".join(map(str, prompts[0])), "--prompt-ids", "9", "--max-new-tokens", "6",
+                          "--num-blocks", "32", "--block-tokens", "4", "--max-batch", "2", "--prefill-chunk", "3"],
+                         capture_output=True, text=True, cwd=ROOT, check=True)
+    result = json.loads(out.stdout.strip().splitlines()[-1])
+    for prompt, tokens in zip(prompts, result["generated"]):
+        sequence = list(prompt)
+        assert len(tokens) == 6
+        for token in tokens:
+            logits = plain.forward(raw, weights, sequence)[0][-1]
+            top = torch.topk(logits, 2).values
+            if top[0] - top[1] > 1e-3 * logits.abs().max():
+                assert token == int(logits.argmax())
+            sequence.append(token)
+    out = subprocess.run([sys.executable, "-m", "layover_b200", "--preset", "topidra-tiny", "--random-weights", "--dtype", "bf16",
+                          "--prompt-lens", "9,40", "--max-new-tokens", "4", "--num-blocks", "16"],
+                         capture_output=True, text=True, cwd=ROOT, check=True)
+    assert [len(g) for g in json.loads(out.stdout.strip().splitlines()[-1])["generated"]] == [4, 4]
+    # the replay program as a program: five requests through four state slots, one step at a time
+    requests = {f"q{i}": random_prompt(raw["vocab"], n, seed=60 + i) for i, n in enumerate([12, 30, 7, 19, 25])}
+    steps = mixed(requests, live_limit=4)
+    lines = "".join(json.dumps(s) + "\n" for s in steps)
+    run = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(tmp_path),
+                          "--max-tokens", str(max_live_tokens(steps)), "--block-tokens", "4"],
+                         input=lines, capture_output=True, text=True, cwd=ROOT, check=True)
+    assert [l for l in run.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    from replay_helpers import collect
+    compare(collect(steps, tmp_path), {rid: plain.forward(raw, weights, tokens)[0] for rid, tokens in requests.items()},
+            torch.float32)
