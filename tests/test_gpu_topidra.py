@@ -127,7 +127,9 @@ def plain_identity_attention(rows, sizes, heads, kv, d, e, sink, scale, window):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES.values()))
-@pytest.mark.parametrize("heads,kv,d,e,window", [(4, 2, 16, 8, 12), (2, 2, 8, 20, 5), (3, 1, 12, 12, 64)])
+@pytest.mark.parametrize("heads,kv,d,e,window", [(4, 2, 16, 8, 12), (2, 2, 8, 20, 5), (3, 1, 12, 12, 64),
+                                                 # multiples of 16: the tensor-core kernels in bfloat16
+                                                 (4, 2, 32, 16, 12), (2, 1, 16, 48, 9), (8, 2, 64, 64, 30), (3, 3, 128, 128, 17)])
 def test_sink_attention_sees_exactly_its_window(dtype, heads, kv, d, e, window):
     """One key gets a score far above all others: the newest the window still holds, the first it
     has dropped, keys at page borders, the very first key; as a prompt and with the query decoded."""
@@ -236,13 +238,15 @@ def folders(tmp_path_factory):
     out = {}
     for index, (name, raw) in enumerate(CONFIGS.items()):
         folder = tmp_path_factory.mktemp(f"topidra-{name}")
-        lb.write_model_folder(lb.TopidraConfig.from_hf_dict(raw), folder, seed=40 + index, **INIT)
+        # seeded by the name, so that a new configuration does not change the others' weights
+        lb.write_model_folder(lb.TopidraConfig.from_hf_dict(raw), folder, seed=sum(map(ord, name)), **INIT)
         out[name] = (folder, json.loads((folder / "config.json").read_text()), load_file(str(folder / "model.safetensors")))
     return out
 
 
 LENGTHS = [1, 9, 70, 130, 33, 300]      # the longest is long enough for the segmented scan when it comes whole
 _expected = {}
+_moved = {}
 
 
 def requests_for(name):
@@ -256,7 +260,16 @@ def expected(folders, name):
     return _expected[name]
 
 
-def compare(rows, want, dtype):
+def moved_by_rounding(folders, name):
+    """Per request: how far rounding what a bfloat16 run stores moves each row of the plain model's logits."""
+    if name not in _moved:
+        _, raw, weights = folders[name]
+        _moved[name] = {rid: plain.forward(raw, weights, tokens, plain.through_bfloat16)[0] - expected(folders, name)[rid]
+                        for rid, tokens in requests_for(name).items()}
+    return _moved[name]
+
+
+def compare(rows, want, dtype, moved=None):
     for rid, reference in want.items():
         assert sorted(rows[rid]) == list(range(reference.shape[0])), f"{rid}: rows missing"
         got = torch.from_numpy(np.stack([rows[rid][p] for p in range(reference.shape[0])])).to(F)
@@ -267,6 +280,11 @@ def compare(rows, want, dtype):
             # window off by one or a missing sink changes a row by about its own size), and four times
             # that for the row's largest error.
             bound = reference.pow(2).mean(dim=1).sqrt() / 16
+            if moved is not None:
+                # ... unless the row is ill-conditioned in the plain model itself (a first token whose q . k is
+                # near zero before a norm that restores the scale): then three times what one rounding of
+                # the stored tensors does to the plain model's row
+                bound = torch.maximum(bound, 3 * moved[rid].pow(2).mean(dim=1).sqrt())
             worst = torch.maximum((got - reference).pow(2).mean(dim=1).sqrt(), (got - reference).abs().max(dim=1).values / 4)
         else:
             worst = (got - reference).abs().max(dim=1).values
@@ -287,7 +305,8 @@ def test_every_cut_matches_the_plain_implementation(folders, tmp_path, name, dty
         assert max_live_tokens(steps) < sum(-(-n // 64) * 64 for n in LENGTHS)
         assert max(len(s["entries"]) for s in steps) == 4
     rows = run_trace(folder, dtype_name, steps, tmp_path, block_tokens=PAGES[name], max_requests=4)
-    compare(rows, expected(folders, name), DTYPES[dtype_name])
+    compare(rows, expected(folders, name), DTYPES[dtype_name],
+            moved_by_rounding(folders, name) if dtype_name == "bfloat16" else None)
 
 
 @pytest.mark.parametrize("name", ["mid_loop", "front_loop"])

@@ -39,9 +39,17 @@ CONFIGS = {
         attention(2, 2, 20, 36, 500, 0.2),
         lightning(2, 40, 20, [0.99, 0.6], ff=56),
     ]),
+    # head sizes that are multiples of 16: in bfloat16 the attention runs on the tensor-core kernels, with keys
+    # and values of different sizes on pages of the larger one; four query heads per key/value head
+    "wide_heads": config(120, 64, [
+        attention(4, 1, 32, 16, 24, 0.2, ff=64),
+        lightning(2, 32, 16, [0.9, 0.97]),
+        attention(2, 2, 16, 64, 10, 0.3),
+        attention(4, 2, 48, 48, 70, 0.15, ff=48),
+    ], loop=(0, 2, 2)),
     # only linear layers: no pages anywhere; only attention layers: no state anywhere
     "linear_only": config(64, 32, [lightning(2, 8, 16, 0.97, ff=48), lightning(1, 36, 8, [0.75])], loop=(0, 1, 2)),
     "softmax_only": config(80, 32, [attention(2, 1, 16, 16, 9, 0.3, ff=40), attention(4, 4, 8, 12, 33, 0.4)], loop=(1, 2, 2)),
 }
-PAGES = {"mid_loop": 4, "front_loop": 16, "no_loop": 8, "linear_only": 16, "softmax_only": 2}
+PAGES = {"mid_loop": 4, "front_loop": 16, "no_loop": 8, "wide_heads": 16, "linear_only": 16, "softmax_only": 2}
 INIT = dict(std=0.25, norm_std=0.3)
