@@ -129,7 +129,8 @@ def plain_identity_attention(rows, sizes, heads, kv, d, e, sink, scale, window):
 @pytest.mark.parametrize("dtype", list(DTYPES.values()))
 @pytest.mark.parametrize("heads,kv,d,e,window", [(4, 2, 16, 8, 12), (2, 2, 8, 20, 5), (3, 1, 12, 12, 64),
                                                  # multiples of 16: the tensor-core kernels in bfloat16
-                                                 (4, 2, 32, 16, 12), (2, 1, 16, 48, 9), (8, 2, 64, 64, 30), (3, 3, 128, 128, 17)])
+                                                 (4, 2, 32, 16, 12), (2, 1, 16, 48, 9), (8, 2, 64, 64, 30), (3, 3, 128, 128, 17),
+                                                 (2, 1, 160, 256, 20), (2, 2, 144, 144, 6)])
 def test_sink_attention_sees_exactly_its_window(dtype, heads, kv, d, e, window):
     """One key gets a score far above all others: the newest the window still holds, the first it
     has dropped, keys at page borders, the very first key; as a prompt and with the query decoded."""
@@ -186,7 +187,8 @@ def identity_linear(heads, d, e, decay):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES.values()))
-@pytest.mark.parametrize("heads,d,e,decay", [(2, 16, 8, [0.999, 0.6]), (1, 40, 36, 0.98), (3, 4, 70, [1.0, 0.5, 0.9])])
+@pytest.mark.parametrize("heads,d,e,decay", [(2, 16, 8, [0.999, 0.6]), (1, 40, 36, 0.98), (3, 4, 70, [1.0, 0.5, 0.9]),
+                                             (2, 128, 64, [0.99, 0.0]), (1, 200, 40, 0.95)])
 def test_decay_scan_carries_its_state_across_any_cut(dtype, heads, d, e, decay):
     """A key hundreds of tokens back still decides the output under a slow decay; the same rows as a
     prompt, in portions down to two tokens and decoded one by one, beside another request."""
