@@ -75,18 +75,18 @@ def test_every_pass_has_a_cache_or_state_of_its_own():
     raw = CONFIGS["mid_loop"]
     model = assemble(spec_for_config(lb.TopidraConfig.from_hf_dict(raw)))
     needs = model.cache_needs()
-    assert len(needs) == 8 and all(reads is None for _, _, reads in needs)
+    assert len(needs) == 10 and all(reads is None for _, _, reads in needs)
     cache = CacheManager(needs, 12, 4, torch.float32, "cpu", max_requests=3)
-    # layers 1 and 2 run three times: three state layers and three page layers of their kinds
+    # layers 1 and 2 run four times: four state layers and four page layers of their kinds
     by_need = {g.need: g.entries for g in cache.paged + cache.states}
-    assert by_need[StateNeed((1, 24, 40), torch.float32)] == [1, 3, 5]
-    assert by_need[PagedKVNeed(2, 16, 12, 8)] == [2, 4, 6]
-    assert by_need[PagedKVNeed(1, 8, 7, 16)] == [7]
+    assert by_need[StateNeed((1, 24, 40), torch.float32)] == [1, 3, 5, 7]
+    assert by_need[PagedKVNeed(2, 16, 12, 8)] == [2, 4, 6, 8]
+    assert by_need[PagedKVNeed(1, 8, 7, 16)] == [9]
     assert by_need[StateNeed((2, 16, 8), torch.float32)] == [0]
     group = next(g for g in cache.paged if g.need.v_head_dim == 8)
-    assert group.pool is None and group.k_store.shape == (3, 13, 2, 4, 16) and group.v_store.shape == (3, 13, 2, 4, 8)
-    views = {cache.view(i).state.data_ptr() for i in (1, 3, 5)}
-    assert len(views) == 3
+    assert group.pool is None and group.k_store.shape == (4, 13, 2, 4, 16) and group.v_store.shape == (4, 13, 2, 4, 8)
+    views = {cache.view(i).state.data_ptr() for i in (1, 3, 5, 7)}
+    assert len(views) == 4
 
 
 def test_windows_give_pages_back_and_slots_are_zeroed_on_reuse():

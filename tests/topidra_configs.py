@@ -21,13 +21,13 @@ def config(vocab, width, layers, loop=(0, 0, 1), eps=1e-6):
 
 
 CONFIGS = {
-    # both mixers, a span in the middle that runs three times and begins with a linear layer
+    # both mixers, a span in the middle that runs four times and begins with a linear layer
     "mid_loop": config(211, 64, [
         lightning(2, 16, 8, [0.8, 0.995], ff=96),
         lightning(1, 24, 40, 0.9),
         attention(4, 2, 16, 8, 12, 0.3, ff=80),
         attention(2, 1, 8, 16, 7, 0.5),
-    ], loop=(1, 3, 3)),
+    ], loop=(1, 3, 4)),
     # the span starts at layer 0 with an attention layer and ends the model; a window of 1; one head
     "front_loop": config(150, 48, [
         attention(3, 3, 12, 12, 21, 0.25, ff=72),
