@@ -12,7 +12,9 @@ that is never handed out: padded rows of a captured decode step and table entrie
 was given back point at it.
 
 A group with a window only keeps the pages that a later query can still see: after a step,
-pages that lie wholly below `tokens - window + 1` go back to the free list and are reused.
+pages that lie wholly below `tokens - window + 1` go back to the free list and are reused. A group
+with a chunked mask (a query sees only the keys of its own chunk of positions) gives back the pages
+that lie wholly before the chunk of the next token.
 State groups own `[slots + 1, *shape]`; a request's slot is zeroed when it is opened.
 
 Beside the mixers' state every request has one *record* of `record_words` int32 words on the
@@ -198,6 +200,9 @@ class CacheManager:
 
     def _first_needed_page(self, group: PagedGroup, first_query: int) -> int:
         """Pages below this index hold no key that a query at `first_query` or later can see."""
+        chunk = getattr(group.need, "chunk", None)
+        if chunk:       # a query sees only its own chunk: everything before the chunk of `first_query` is done with
+            return (first_query // chunk * chunk) // self.block_tokens
         if group.need.window is None:
             return 0
         return max(0, first_query - group.need.window + 1) // self.block_tokens
@@ -206,9 +211,10 @@ class CacheManager:
         """The most pages of a group that a request of `total_tokens` holds at any time when it is
         fed at most `chunk` tokens a step."""
         group = self.paged[group_index]
-        if group.need.window is None:
+        reach = getattr(group.need, "chunk", None) or group.need.window     # the most keys behind a query that stay visible
+        if reach is None:
             return self.blocks_for(total_tokens)
-        span = min(total_tokens, group.need.window - 1 + max(1, chunk))
+        span = min(total_tokens, reach - 1 + max(1, chunk))
         return min(self.blocks_for(total_tokens), span // self.block_tokens + 2)
 
     def blocks_missing(self, seq: SequenceCache, new_total: int) -> list[int]:

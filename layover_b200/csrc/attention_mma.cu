@@ -7,7 +7,8 @@
 // Two kernels share the tile code:
 //   prefill  one block per (tile of 64 queries of one sequence, query head); its four warps own 16
 //            query rows each and walk the keys in tiles of 64 with a two-stage cp.async pipeline;
-//            the causal mask (and a window) is applied from absolute positions.
+//            the causal mask (and a window, or a chunked mask: `window` < 0 lets a query see only the
+//            keys of its own chunk of -window positions) is applied from absolute positions.
 //   decode   one block per (sequence with a single new token, KV head, split of the context); the
 //            query heads that share the KV head are the rows of one 16-row MMA tile, so every key
 //            and value is read once for the whole group; the four warps take 16 keys each of every
@@ -205,7 +206,8 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[MAX_DIM / 16][4],
         if (!UPPER && e >= 2) continue;
         const int key = key0 + n * 8 + 2 * t + (e & 1);
         const int p = e < 2 ? p0 : p1;
-        const bool seen = key <= p && key >= key_lo && (window <= 0 || p - key < window);
+        const bool seen = key <= p && key >= key_lo && (window <= 0 || p - key < window) &&
+                          (window >= 0 || key >= p / -window * -window);
         if (!seen) s[n][e] = -INFINITY;
       }
     }
@@ -311,7 +313,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
   const int dk = dim >> 4;
 
   const int p_first = start + q0, p_last = p_first + n_q - 1;
-  const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  // window > 0: the last `window` keys; window < 0: the keys of the query's own chunk of -window positions
+  const int key_lo = window > 0 ? max(0, p_first - window + 1) : (window < 0 ? p_first / -window * -window : 0);
   const int tile_lo = key_lo / BKEYS, tile_hi = p_last / BKEYS;
   const TableSlice pages = cache_table(table_cache, TABLE_CACHE, table, key_lo, p_last, page_tokens);
   const TileShape shape{kv_heads, kv_head, dim, page_tokens, chunk_shift, page_shift};
@@ -362,7 +365,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     if (tile * BKEYS <= p_warp + 15) {
       // every row of the warp sees the whole tile unless it reaches past the first row's position,
       // starts before the first visible key or a window cuts it
-      const bool masked = tile * BKEYS + BKEYS - 1 > p_warp || tile * BKEYS < key_lo || window > 0;
+      const bool masked = tile * BKEYS + BKEYS - 1 > p_warp || tile * BKEYS < key_lo || window != 0;
       warp_tile<MAX_DIM, EXACT, BKEYS / 16, true, SINK>(qf, k_base + buf * buf_bytes, v_base + buf * buf_bytes, dim, o, m_run,
                                                         l_run, masked, tile * BKEYS, p0, p1, key_lo, window, scale_log2, t);
     }
@@ -440,7 +443,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   const int* table = block_table + (size_t)seq * table_width;
   const int dk = dim >> 4;
 
-  const int key_lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int key_lo = window > 0 ? max(0, p - window + 1) : (window < 0 ? p / -window * -window : 0);
   const int first_tile = key_lo / BKEYS, n_tiles = p / BKEYS + 1 - first_tile;
   const int per_split = (n_tiles + splits - 1) / splits;
   const int tile_begin = first_tile + split * per_split;

@@ -2,9 +2,11 @@
 // for every segment length: a whole prompt, a portion of one, or a single decoded token.
 //
 //   s_j = (q . K_j) * scale          for keys j <= p and (window == 0 or p - j < window)
+//                                    and (mask_chunk == 0 or floor(j / mask_chunk) == floor(p / mask_chunk))
 //   o   = sum_j softmax(s)_j V_j     (layover/model.py:59,90-96; layover/kernels/triton_decode.py:89-119)
 //
-// where p is the query's absolute position. Three optional generalisations, each off with a null
+// where p is the query's absolute position (a chunked mask lets a query see only the keys of its own
+// chunk of mask_chunk positions, counted from position 0 of the sequence). Three optional generalisations, each off with a null
 // pointer or an equal size: values of another size than keys (`vdim`, out is [T, q_heads * vdim]);
 // a learned sink per query head, a score without key or value that only enlarges the softmax's
 // denominator, o = sum_j exp(s_j) V_j / (exp(sink_h) + sum_j exp(s_j)); and a gate per (token,
@@ -51,7 +53,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
                             const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                             const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int q_heads,
                             int kv_heads, int dim, int page_tokens, float scale, int window, int vdim,
-                            const float* __restrict__ sinks, const float* __restrict__ gates) {
+                            const float* __restrict__ sinks, const float* __restrict__ gates, int mask_chunk) {
   extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -73,7 +75,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
   }
 
   const int p_first = start + q0, p_last = start + q0 + n_q - 1;
-  const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;  // first key any row here may see
+  int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;        // first key any row here may see
+  if (mask_chunk > 0) key_lo = max(key_lo, p_first / mask_chunk * mask_chunk);
   const int tile_lo = key_lo / BKEYS, tile_hi = p_last / BKEYS;
 
   float m[ROWS_PER_WARP], l[ROWS_PER_WARP], acc[ROWS_PER_WARP][ACC_PER_LANE];
@@ -117,7 +120,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
       const int row = warp * ROWS_PER_WARP + r;
       if (row >= n_q) continue;  // uniform over the warp
       const int p = p_first + row;
-      const bool seen = key <= p && (window <= 0 || p - key < window);
+      const bool seen = key <= p && (window <= 0 || p - key < window) && (mask_chunk <= 0 || key >= p / mask_chunk * mask_chunk);
       float s = 0.f;
       const float* qr = q_s + row * dim;
       const float* kr = k_s + lane * (dim + 1);
@@ -173,7 +176,7 @@ LB_EXPORT int lb_attention_simt(int dtype, const void* q, const void* k_pool, co
                                 const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
                                 const int* tile_seq, const int* tile_q0, int n_tiles, int q_heads, int kv_heads,
                                 int dim, int page_tokens, float scale, int window, int vdim, const float* sinks,
-                                const float* gates, cudaStream_t stream) {
+                                const float* gates, int mask_chunk, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (dim <= 0 || dim > MAX_DIM || dim % 4 || kv_heads <= 0 || q_heads % kv_heads || q_heads > 65535) return LB_ERR_SIZE;
   if (vdim <= 0 || vdim > MAX_DIM || vdim % 4) return LB_ERR_SIZE;
@@ -185,13 +188,13 @@ LB_EXPORT int lb_attention_simt(int dtype, const void* q, const void* k_pool, co
       cudaFuncSetAttribute(paged_attention_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     lb_launch(paged_attention_simt_kernel<float>, grid, WARPS * 32, smem, stream, 
         (const float*)q, (const float*)k_pool, (const float*)v_pool, (float*)out, block_table, table_width, cu_q,
-        ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates);
+        ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates, mask_chunk);
   } else if (dtype == LB_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(paged_attention_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     lb_launch(paged_attention_simt_kernel<bf16>, grid, WARPS * 32, smem, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates);
+        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates, mask_chunk);
   } else
     return LB_ERR_DTYPE;
   return lb_last_error();

@@ -35,6 +35,7 @@ SOURCES: dict[str, tuple[str, tuple[str, ...]]] = {
     "gemm_simt": ("gemm_simt.cu", ()),
     "attention_simt": ("attention_simt.cu", ()),
     "linear_attention": ("linear_attention.cu", ()),
+    "moe": ("moe.cu", ()),
     "sampling": ("sampling.cu", ()),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ()),
     "attention_mma": ("attention_mma.cu", ()),

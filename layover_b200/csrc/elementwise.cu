@@ -759,3 +759,244 @@ LB_EXPORT int lb_qk_rownorm_kv(int dtype, const void* proj, long row_stride, voi
     return LB_ERR_DTYPE;
   return lb_last_error();
 }
+
+// ---------------------------------------------------------------- 32-bit residual stream: add + LayerNorm
+// For blocks whose sub-layers all read ONE norm of the stream and whose outputs are added together
+// (a parallel block): the stream takes up to two not-yet-added outputs at once,
+//   v      = x[row] + delta_a[row] + delta_b[row]          (either may be null)
+//   x[row] = v                                             (not with `rows`: then x is only read)
+//   out[r] = T((v - mean(v)) * rsqrt(mean((v - mean(v))^2) + eps) * weight + bias)   (weight null: only the sum)
+// in 32-bit, rounded once at the store of out. The variance is the mean of the squared deviations
+// from the mean (two passes over the row, which sits in shared memory). One block per row; the
+// block size depends on the width only, so a row's sums do not depend on the batch.
+template <typename T>
+__global__ void residual_layernorm_kernel(float* __restrict__ x, const T* __restrict__ delta_a,
+                                          const T* __restrict__ delta_b, const float* __restrict__ weight,
+                                          const float* __restrict__ bias, T* __restrict__ out,
+                                          const int* __restrict__ rows, int hidden, float eps) {
+  extern __shared__ float row_vals[];  // hidden floats + 33 for the reductions
+  pdl_launch_dependents();
+  pdl_wait();
+  float* scratch = row_vals + hidden;
+  const size_t src = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+  float* xr = x + src * hidden;
+  const T* ar = delta_a ? delta_a + src * hidden : nullptr;
+  const T* br = delta_b ? delta_b + src * hidden : nullptr;
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = xr[i];
+    if (ar && br) v += Elem<T>::load(ar + i) + Elem<T>::load(br + i);   // the sub-layers' sum joins the stream
+    else if (ar) v += Elem<T>::load(ar + i);
+    else if (br) v += Elem<T>::load(br + i);
+    if (!rows && (ar || br)) xr[i] = v;
+    row_vals[i] = v;
+    sum += v;
+  }
+  if (!weight) return;
+  const float mean = block_sum(sum, scratch) / (float)hidden;
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float d = row_vals[i] - mean;
+    sq += d * d;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)hidden + eps);
+  T* o = out + (size_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    Elem<T>::store(o + i, (row_vals[i] - mean) * inv * weight[i] + (bias ? bias[i] : 0.f));
+}
+
+LB_EXPORT int lb_residual_layernorm(int dtype, float* x, const void* delta_a, const void* delta_b, const float* weight,
+                                    const float* bias, void* out, const int* rows, int n_rows, int hidden, float eps,
+                                    cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (hidden <= 0 || (weight && !out)) return LB_ERR_SIZE;
+  static LbPerDeviceOnce once;
+  const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+  if (smem > 200 * 1024) return LB_ERR_SIZE;
+  if (smem > 48 * 1024 && once.first()) {
+    cudaFuncSetAttribute(residual_layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(residual_layernorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  }
+  const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+  if (dtype == LB_F32)
+    lb_launch(residual_layernorm_kernel<float>, n_rows, threads, smem, stream, x, (const float*)delta_a,
+              (const float*)delta_b, weight, bias, (float*)out, rows, hidden, eps);
+  else if (dtype == LB_BF16)
+    lb_launch(residual_layernorm_kernel<bf16>, n_rows, threads, smem, stream, x, (const bf16*)delta_a, (const bf16*)delta_b,
+              weight, bias, (bf16*)out, rows, hidden, eps);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
+// ---------------------------------------------------------------- biases + partial rotation + value blend + KV write
+// For attention whose projections have biases, whose rotation covers only the first `2 n_freq`
+// channels of a head, and whose values may be blended with the values that an earlier layer made
+// for the same token. A token's row of the stacked projection, in 32-bit whatever the run's type, is
+//   [ q: q_heads * dim | k: kv_heads * dim | v: kv_heads * vdim | ... ].
+//   q, k, v += their biases                                              (each null: none)
+//   channels i and i + n_freq of every q and k head (i < n_freq) turn by the token's angle i:
+//       (u, w) -> (u cos - w sin, w cos + u sin), cos/sin from table[t] ([T, 2, n_freq]; null: no rotation)
+//   values: blend 1 stores v (with its bias) to first_v[t] ([T, kv_heads * vdim] floats) and uses it as it is;
+//           blend 2 uses (1 - lambda) v + lambda first_v[t]; blend 0 uses v
+//   q_out[t] = T(q), k page = T(k), v page = T(v), laid out and zero-filled up to each tensor's room per
+//   head as in the whole-row kernel above.
+// One block per token; all arithmetic 32-bit, rounded once at the stores.
+template <typename T>
+__global__ void heads_bias_rope_kv_kernel(const float* __restrict__ proj, long row_stride, T* __restrict__ q_out,
+                                          T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                          const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+                                          const float* __restrict__ v_bias, const float* __restrict__ table, int n_freq,
+                                          const int* __restrict__ slot_map, float* __restrict__ first_v, int blend,
+                                          const float* __restrict__ lambda, int q_heads, int kv_heads, int dim, int vdim,
+                                          int page_tokens, int q_room, int k_room, int v_room) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, nq = q_heads * dim, nk = kv_heads * dim;
+  const float* row = proj + (size_t)t * row_stride;
+  const float* cs = table ? table + (size_t)t * 2 * n_freq : nullptr;
+  const float* sn = cs ? cs + n_freq : nullptr;
+  const int rotated = cs ? 2 * n_freq : 0;
+  const int slot = slot_map[t];
+  const size_t page = (size_t)(slot / page_tokens), in_page = (size_t)(slot % page_tokens);
+  // q and k heads share one loop: head index h over q_heads + kv_heads
+  const int qk_items = q_heads * q_room + kv_heads * k_room;
+  for (int i = threadIdx.x; i < qk_items; i += blockDim.x) {
+    const bool is_q = i < q_heads * q_room;
+    const int j = is_q ? i : i - q_heads * q_room;
+    const int room = is_q ? q_room : k_room;
+    const int h = j / room, c = j - h * room;
+    const float* src = row + (is_q ? 0 : nq) + h * dim;
+    const float* b = is_q ? q_bias : k_bias;
+    if (b) b += h * dim;
+    float v = 0.f;
+    if (c < dim) {
+      v = src[c] + (b ? b[c] : 0.f);
+      if (c < rotated) {
+        const int f = c < n_freq ? c : c - n_freq;
+        const int other = c < n_freq ? c + n_freq : c - n_freq;
+        const float w = src[other] + (b ? b[other] : 0.f);
+        v = c < n_freq ? v * cs[f] - w * sn[f] : v * cs[f] + w * sn[f];
+      }
+    }
+    if (is_q) Elem<T>::store(q_out + (size_t)t * q_heads * q_room + j, v);
+    else Elem<T>::store(k_pool + ((page * kv_heads + h) * page_tokens + in_page) * k_room + c, v);
+  }
+  const float lam = blend == 2 ? *lambda : 0.f;
+  for (int i = threadIdx.x; i < kv_heads * v_room; i += blockDim.x) {
+    const int g = i / v_room, c = i - g * v_room;
+    float v = 0.f;
+    if (c < vdim) {
+      const int at = g * vdim + c;
+      v = row[nq + nk + at] + (v_bias ? v_bias[at] : 0.f);
+      if (blend == 1) first_v[(size_t)t * kv_heads * vdim + at] = v;
+      else if (blend == 2) v = (1.f - lam) * v + lam * first_v[(size_t)t * kv_heads * vdim + at];
+    }
+    Elem<T>::store(v_pool + ((page * kv_heads + g) * page_tokens + in_page) * v_room + c, v);
+  }
+}
+
+LB_EXPORT int lb_heads_bias_rope_kv(int dtype, const float* proj, long row_stride, void* q_out, void* k_pool, void* v_pool,
+                                    const float* q_bias, const float* k_bias, const float* v_bias, const float* table,
+                                    int n_freq, const int* slot_map, float* first_v, int blend, const float* lambda,
+                                    int tokens, int q_heads, int kv_heads, int dim, int vdim, int page_tokens, int q_room,
+                                    int k_room, int v_room, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (q_heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || page_tokens <= 0 || q_room < dim || k_room < dim ||
+      v_room < vdim || n_freq < 0 || 2 * n_freq > dim || blend < 0 || blend > 2 || (blend && !first_v) ||
+      (blend == 2 && !lambda))
+    return LB_ERR_SIZE;
+  const int threads = q_heads * dim >= 1024 ? 256 : 128;
+  if (dtype == LB_F32)
+    lb_launch(heads_bias_rope_kv_kernel<float>, tokens, threads, 0, stream, proj, row_stride, (float*)q_out, (float*)k_pool,
+              (float*)v_pool, q_bias, k_bias, v_bias, table, n_freq, slot_map, first_v, blend, lambda, q_heads, kv_heads, dim,
+              vdim, page_tokens, q_room, k_room, v_room);
+  else if (dtype == LB_BF16)
+    lb_launch(heads_bias_rope_kv_kernel<bf16>, tokens, threads, 0, stream, proj, row_stride, (bf16*)q_out, (bf16*)k_pool,
+              (bf16*)v_pool, q_bias, k_bias, v_bias, table, n_freq, slot_map, first_v, blend, lambda, q_heads, kv_heads, dim,
+              vdim, page_tokens, q_room, k_room, v_room);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
+// ---------------------------------------------------------------- a sigmoid gate per channel of the heads' outputs
+// out[t, h * vdim + c] = T(heads[t, h * room + c] * sigmoid(logits[t, h * vdim + c])): the gate of every
+// channel of the concatenated heads, from 32-bit logits that sit in a wider row (`logit_stride` floats
+// a token); the heads may come padded to `room` channels each, the output is dense.
+template <typename T>
+__global__ void channel_gate_kernel(const T* __restrict__ heads, const float* __restrict__ logits, long logit_stride,
+                                    T* __restrict__ out, long total, int q_heads, int vdim, int room) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int width = q_heads * vdim;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / width;
+    const int j = (int)(i - t * width), h = j / vdim, c = j - h * vdim;
+    const float gate = 1.0f / (1.0f + expf(-logits[t * logit_stride + j]));
+    Elem<T>::store(out + i, Elem<T>::load(heads + (t * q_heads + h) * room + c) * gate);
+  }
+}
+
+LB_EXPORT int lb_channel_gate(int dtype, const void* heads, const float* logits, long logit_stride, void* out, int tokens,
+                              int q_heads, int vdim, int room, cudaStream_t stream) {
+  const long total = (long)tokens * q_heads * vdim;
+  if (total <= 0) return 0;
+  if (room < vdim) return LB_ERR_SIZE;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == LB_F32)
+    lb_launch(channel_gate_kernel<float>, blocks, threads, 0, stream, (const float*)heads, logits, logit_stride, (float*)out,
+              total, q_heads, vdim, room);
+  else if (dtype == LB_BF16)
+    lb_launch(channel_gate_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)heads, logits, logit_stride, (bf16*)out,
+              total, q_heads, vdim, room);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
+// ---------------------------------------------------------------- plain activations and the logits' soft cap
+// out = act(in) element by element: 0 relu(z)^2, 1 gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))),
+// 2 silu(z). 32-bit arithmetic, rounded once.
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, long total, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const float z = Elem<T>::load(in + i);
+    float y;
+    if (act == 0) { const float r = fmaxf(z, 0.f); y = r * r; }
+    else if (act == 1) y = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    else y = z / (1.f + expf(-z));
+    Elem<T>::store(out + i, y);
+  }
+}
+
+LB_EXPORT int lb_activation(int dtype, const void* in, void* out, long total, int act, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (act < 0 || act > 2) return LB_ERR_SIZE;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == LB_F32) lb_launch(activation_kernel<float>, blocks, threads, 0, stream, (const float*)in, (float*)out, total, act);
+  else if (dtype == LB_BF16) lb_launch(activation_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)in, (bf16*)out, total, act);
+  else return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
+// logits <- cap * tanh(logits / cap), in place, 32-bit.
+__global__ void softcap_kernel(float* __restrict__ logits, long total, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x)
+    logits[i] = cap * tanhf(logits[i] / cap);
+}
+
+LB_EXPORT int lb_softcap(float* logits, long total, float cap, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (!(cap > 0.f)) return LB_ERR_SIZE;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  lb_launch(softcap_kernel, blocks, threads, 0, stream, logits, total, cap);
+  return lb_last_error();
+}

@@ -1,0 +1,330 @@
+// Routed experts: a router that sends every token to its `top` best experts, the grouping of the
+// (token, expert) pairs by expert, the experts' two matrix products over those groups, and the sum
+// of a token's expert outputs. Nothing here returns to the host between the steps: the group sizes
+// stay on the device and the products are launched for the largest number of tiles the pairs can make.
+//
+//   route     z = W_router h in 32-bit, one warp per token; score = sigmoid(z); the `top` largest z
+//             (ties: the lower index) with their scores; optionally one more 32-bit dot product per
+//             token, sigmoid(w_shared . h), the factor of a shared expert
+//   group     offsets[e] .. offsets[e + 1] = the places of expert e's pairs in `order`, order[place] =
+//             pair = token * top + k
+//   products  for every expert e and every pair in its group
+//               up    act[place]  = T(act_fn(s * (Wg_e h)) * (s * (Wu_e h)))   s = the pair's score
+//               down  y[pair]     = Wd_e act[place]                             (32-bit)
+//             The score multiplies the expert's INPUT; W (s h) = s (W h), and the factor is applied to
+//             the 32-bit sums rather than to a rounded s h. Every output element is one dot product
+//             summed in the order of k, so it does not depend on where its row sits in a tile or on
+//             what else is in the batch. (For designs that weight the expert's output the same
+//             kernels serve: up with s = 1, the weight in `combine`.)
+//   combine   out[t] = T(sum_k y[t * top + k] * (c_k) + f_t * shared[t]), c_k = 1 or the pair's score
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROUTE_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ shared_w,
+                 int* __restrict__ ids, float* __restrict__ scores, float* __restrict__ shared_factor, int tokens,
+                 int hidden, int experts, int top) {
+  extern __shared__ float logits[];                 // [ROUTE_WARPS][experts]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= tokens) return;
+  const T* row = h + (size_t)t * hidden;
+  float* z = logits + warp * experts;
+  for (int e = 0; e < experts; ++e) {
+    const float* w = router + (size_t)e * hidden;
+    float s = 0.f;
+    for (int i = lane; i < hidden; i += 32) s = fmaf(Elem<T>::load(row + i), w[i], s);
+    s = warp_sum(s);
+    if (lane == 0) z[e] = s;
+  }
+  if (shared_w) {
+    float s = 0.f;
+    for (int i = lane; i < hidden; i += 32) s = fmaf(Elem<T>::load(row + i), shared_w[i], s);
+    s = warp_sum(s);
+    if (lane == 0) shared_factor[t] = 1.0f / (1.0f + expf(-s));
+  }
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = z[e];
+      if (v > best || (v == best && e < at)) { best = v; at = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at >= experts) at = k;                      // only when every logit left is NaN or -inf
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = at;
+      scores[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
+      z[at] = -INFINITY;                            // taken
+    }
+    __syncwarp();
+  }
+}
+
+// One block: count, scan, place. The order inside a group is the order of arrival; no result depends on it.
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ offsets, int* __restrict__ order) {
+  extern __shared__ int counts[];                   // [experts] counts, then [experts] cursors
+  pdl_launch_dependents();
+  pdl_wait();
+  int* cursor = counts + experts;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&counts[ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts; ++e) {
+      offsets[e] = run;
+      cursor[e] = run;
+      run += counts[e];
+    }
+    offsets[experts] = run;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) order[atomicAdd(&cursor[ids[i]], 1)] = i;
+}
+
+template <int ACT> __device__ __forceinline__ float expert_activation(float g) {
+  if (ACT == 1) return fmaxf(g, 0.f);
+  return g / (1.0f + expf(-g));      // silu
+}
+
+// The experts' products on the FFMA pipes (both precisions; 32-bit sums). A block owns BM places of one
+// expert's group and BN output columns; a thread TM x TN of them. The k loop runs in steps of BK through
+// shared memory, every element's sum in the order of k.
+//   GATED: two weight tiles (gate rows w, up rows w + n_out * k_dim); out = T(act(s g) * (s u)), s = pair_scale[pair]
+//   else:  out (float) = the plain product
+// `a_rows`: the row of `a` for a place is a_rows[place] / a_div (null: the place itself);
+// `out_rows`: the row of out is out_rows[place] (null: the place itself).
+template <typename T, typename OutT, int BM, int BN, int TM, int TN, bool GATED, int ACT>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+moe_expert_product_kernel(const T* __restrict__ a, long a_stride, const int* __restrict__ a_rows, int a_div,
+                          const int* __restrict__ offsets, int experts, const T* __restrict__ w, long expert_stride,
+                          int n_out, int k_dim, OutT* __restrict__ out, long out_stride,
+                          const int* __restrict__ out_rows, const float* __restrict__ pair_scale,
+                          const int* __restrict__ order) {
+  constexpr int BK = 32, THREADS = (BM / TM) * (BN / TN);
+  __shared__ float a_s[BK][BM + 1];
+  __shared__ float w_s[GATED ? 2 : 1][BK][BN + 1];
+  __shared__ int tile_expert, tile_first, tile_rows;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    int left = blockIdx.x, found = -1, first = 0, rows = 0;
+    for (int e = 0; e < experts && found < 0; ++e) {
+      const int begin = offsets[e], count = offsets[e + 1] - begin, tiles = (count + BM - 1) / BM;
+      if (left < tiles) {
+        found = e;
+        first = begin + left * BM;
+        rows = min(BM, count - left * BM);
+      }
+      left -= tiles;
+    }
+    tile_expert = found; tile_first = first; tile_rows = rows;
+  }
+  __syncthreads();
+  const int expert = tile_expert, first = tile_first, rows = tile_rows;
+  if (expert < 0) return;
+  const int n0 = blockIdx.y * BN;
+  const T* wg = w + (size_t)expert * expert_stride;
+  const int tx = threadIdx.x % (BN / TN), ty = threadIdx.x / (BN / TN);
+  float acc[GATED ? 2 : 1][TM][TN];
+#pragma unroll
+  for (int z = 0; z < (GATED ? 2 : 1); ++z)
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[z][i][j] = 0.f;
+
+  for (int k0 = 0; k0 < k_dim; k0 += BK) {
+    for (int i = threadIdx.x; i < BM * BK; i += THREADS) {
+      const int r = i / BK, c = i - r * BK;
+      float v = 0.f;
+      if (r < rows && k0 + c < k_dim) {
+        const int place = first + r;
+        const long src = a_rows ? a_rows[place] / a_div : place;
+        v = Elem<T>::load(a + src * a_stride + k0 + c);
+      }
+      a_s[c][r] = v;
+    }
+    for (int i = threadIdx.x; i < BN * BK; i += THREADS) {
+      const int r = i / BK, c = i - r * BK;
+      const bool live = n0 + r < n_out && k0 + c < k_dim;
+      w_s[0][c][r] = live ? Elem<T>::load(wg + (size_t)(n0 + r) * k_dim + k0 + c) : 0.f;
+      if (GATED) w_s[1][c][r] = live ? Elem<T>::load(wg + (size_t)(n_out + n0 + r) * k_dim + k0 + c) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < BK; ++k) {
+      float av[TM], bv[GATED ? 2 : 1][TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) av[i] = a_s[k][ty * TM + i];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        bv[0][j] = w_s[0][k][tx + j * (BN / TN)];
+        if (GATED) bv[1][j] = w_s[1][k][tx + j * (BN / TN)];
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+          acc[0][i][j] = fmaf(av[i], bv[0][j], acc[0][i][j]);
+          if (GATED) acc[1][i][j] = fmaf(av[i], bv[1][j], acc[1][i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int r = ty * TM + i;
+    if (r >= rows) continue;
+    const int place = first + r;
+    const long dst = out_rows ? out_rows[place] : place;
+    const float s = (GATED && pair_scale) ? pair_scale[order[place]] : 1.f;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int n = n0 + tx + j * (BN / TN);
+      if (n >= n_out) continue;
+      if (GATED) Elem<OutT>::store(out + dst * out_stride + n, expert_activation<ACT>(s * acc[0][i][j]) * (s * acc[GATED ? 1 : 0][i][j]));
+      else Elem<OutT>::store(out + dst * out_stride + n, acc[0][i][j]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ pair_scale,
+                                   const T* __restrict__ shared_out, const float* __restrict__ shared_factor,
+                                   T* __restrict__ out, long total, int hidden, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / hidden;
+    const int c = (int)(i - t * hidden);
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const float part = y[(t * top + k) * hidden + c];
+      v += pair_scale ? pair_scale[t * top + k] * part : part;
+    }
+    if (shared_out) v += (shared_factor ? shared_factor[t] : 1.f) * Elem<T>::load(shared_out + i);
+    Elem<T>::store(out + i, v);
+  }
+}
+
+template <typename T, bool GATED, typename OutT>
+int launch_product(bool few, int act, const void* a, long a_stride, const int* a_rows, int a_div, const int* offsets,
+                   int experts, const void* w, long expert_stride, int n_out, int k_dim, void* out, long out_stride,
+                   const int* out_rows, const float* pair_scale, const int* order, int n_pairs, cudaStream_t stream) {
+#define LB_MOE_ARGS (const T*)a, a_stride, a_rows, a_div, offsets, experts, (const T*)w, expert_stride, n_out, k_dim, \
+                    (OutT*)out, out_stride, out_rows, pair_scale, order
+  if (few) {      // a handful of rows per expert: tiles of 8 places, so that the weights stream at the memory's rate
+    constexpr int BM = 8, BN = 128;
+    dim3 grid((n_pairs + BM - 1) / BM + experts, (n_out + BN - 1) / BN);
+    if (grid.x > (unsigned)n_pairs) grid.x = n_pairs;   // every tile holds a pair
+    if (act == 1) lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 1, 4, GATED, 1>, grid, 256, 0, stream, LB_MOE_ARGS);
+    else lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 1, 4, GATED, 0>, grid, 256, 0, stream, LB_MOE_ARGS);
+  } else {
+    constexpr int BM = 64, BN = 64;
+    dim3 grid((n_pairs + BM - 1) / BM + experts, (n_out + BN - 1) / BN);
+    if (grid.x > (unsigned)n_pairs) grid.x = n_pairs;
+    if (act == 1) lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 4, 4, GATED, 1>, grid, 256, 0, stream, LB_MOE_ARGS);
+    else lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 4, 4, GATED, 0>, grid, 256, 0, stream, LB_MOE_ARGS);
+  }
+#undef LB_MOE_ARGS
+  return lb_last_error();
+}
+
+}  // namespace
+
+LB_EXPORT int lb_moe_route(int dtype, const void* h, const float* router, const float* shared_w, int* ids, float* scores,
+                           float* shared_factor, int tokens, int hidden, int experts, int top, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (hidden <= 0 || experts <= 0 || top <= 0 || top > experts || experts > 8192 || (shared_w && !shared_factor))
+    return LB_ERR_SIZE;
+  const size_t smem = (size_t)ROUTE_WARPS * experts * sizeof(float);
+  if (smem > 48 * 1024) return LB_ERR_SIZE;
+  const int blocks = (tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
+  if (dtype == LB_F32)
+    lb_launch(moe_route_kernel<float>, blocks, ROUTE_WARPS * 32, smem, stream, (const float*)h, router, shared_w, ids, scores,
+              shared_factor, tokens, hidden, experts, top);
+  else if (dtype == LB_BF16)
+    lb_launch(moe_route_kernel<bf16>, blocks, ROUTE_WARPS * 32, smem, stream, (const bf16*)h, router, shared_w, ids, scores,
+              shared_factor, tokens, hidden, experts, top);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
+LB_EXPORT int lb_moe_group(const int* ids, int n_pairs, int experts, int* offsets, int* order, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (experts <= 0 || experts > 4096) return LB_ERR_SIZE;
+  lb_launch(moe_group_kernel, 1, 1024, (size_t)2 * experts * sizeof(int), stream, ids, n_pairs, experts, offsets, order);
+  return lb_last_error();
+}
+
+// act[place, :] = T(act_fn(s g) * (s u)) for every place of `order`: h [tokens, hidden] (row stride h_stride), gate_up
+// [experts, 2 * inter, hidden] (gate rows, then up rows), scores by pair (null: s = 1). activation 0 silu, 1 relu.
+LB_EXPORT int lb_moe_expert_up(int dtype, const void* h, long h_stride, const int* order, const int* offsets,
+                               const float* scores, const void* gate_up, void* act, int n_pairs, int top, int experts,
+                               int hidden, int inter, int activation, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (experts <= 0 || hidden <= 0 || inter <= 0 || top <= 0 || activation < 0 || activation > 1) return LB_ERR_SIZE;
+  const bool few = n_pairs <= 4 * experts;
+  const long expert_stride = 2L * inter * hidden;
+  if (dtype == LB_F32)
+    return launch_product<float, true, float>(few, activation, h, h_stride, order, top, offsets, experts, gate_up, expert_stride,
+                                              inter, hidden, act, inter, nullptr, scores, order, n_pairs, stream);
+  if (dtype == LB_BF16)
+    return launch_product<bf16, true, bf16>(few, activation, h, h_stride, order, top, offsets, experts, gate_up, expert_stride,
+                                            inter, hidden, act, inter, nullptr, scores, order, n_pairs, stream);
+  return LB_ERR_DTYPE;
+}
+
+// y[pair, :] = down_e act[place, :] in 32-bit: act [n_pairs, inter] by place, down [experts, hidden, inter], y [n_pairs, hidden].
+LB_EXPORT int lb_moe_expert_down(int dtype, const void* act, const int* order, const int* offsets, const void* down, float* y,
+                                 int n_pairs, int experts, int hidden, int inter, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (experts <= 0 || hidden <= 0 || inter <= 0) return LB_ERR_SIZE;
+  const bool few = n_pairs <= 4 * experts;
+  const long expert_stride = (long)hidden * inter;
+  if (dtype == LB_F32)
+    return launch_product<float, false, float>(few, 0, act, inter, nullptr, 1, offsets, experts, down, expert_stride, hidden,
+                                               inter, y, hidden, order, nullptr, order, n_pairs, stream);
+  if (dtype == LB_BF16)
+    return launch_product<bf16, false, float>(few, 0, act, inter, nullptr, 1, offsets, experts, down, expert_stride, hidden,
+                                              inter, y, hidden, order, nullptr, order, n_pairs, stream);
+  return LB_ERR_DTYPE;
+}
+
+// out[t] = T(sum_k c_k y[t * top + k] + f_t shared_out[t]); c_k = pair_scale[t * top + k] or 1; f_t = shared_factor[t] or 1.
+LB_EXPORT int lb_moe_combine(int dtype, const float* y, const float* pair_scale, const void* shared_out,
+                             const float* shared_factor, void* out, int tokens, int hidden, int top, cudaStream_t stream) {
+  const long total = (long)tokens * hidden;
+  if (total <= 0) return 0;
+  if (top <= 0) return LB_ERR_SIZE;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == LB_F32)
+    lb_launch(moe_combine_kernel<float>, blocks, threads, 0, stream, y, pair_scale, (const float*)shared_out, shared_factor,
+              (float*)out, total, hidden, top);
+  else if (dtype == LB_BF16)
+    lb_launch(moe_combine_kernel<bf16>, blocks, threads, 0, stream, y, pair_scale, (const bf16*)shared_out, shared_factor,
+              (bf16*)out, total, hidden, top);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}

@@ -123,7 +123,10 @@ class Model:
         if batch.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
         h = self.final_norm.forward(x, delta, rows=batch.logit_rows)
-        return rt.linear(h, self.head, out_dtype=torch.float32)
+        logits = rt.linear(h, self.head, out_dtype=torch.float32)
+        if self.spec.logit_softcap:
+            ops.softcap(logits, self.spec.logit_softcap)
+        return logits
 
 
 def assemble(spec: ModelSpec, config=None) -> Model:

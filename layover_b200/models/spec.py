@@ -45,6 +45,7 @@ class ModelSpec:
     init_norm_std: float = 0.0
     ignorable_tensors: frozenset = frozenset()
     residual_dtype: str | None = None   # "float32": the residual stream is 32-bit whatever the run's type
+    logit_softcap: float | None = None  # c: the logits leave as c * tanh(logits / c)
 
     def __post_init__(self):
         if not self.schedule:

@@ -272,6 +272,216 @@ def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str, block: 
     return out
 
 
+def residual_layernorm(x: torch.Tensor, delta_a: torch.Tensor | None, delta_b: torch.Tensor | None,
+                       weight: torch.Tensor | None, bias: torch.Tensor | None, eps: float, out: torch.Tensor | None,
+                       rows: torch.Tensor | None = None) -> torch.Tensor | None:
+    """The add + LayerNorm of a 32-bit residual stream x (float32 [T, H], updated in place unless `rows`
+    picks source rows):
+
+        x += delta_a + delta_b                                   (either may be None: two sub-layers' outputs at once)
+        out = (x - mean) * rsqrt(mean((x - mean)^2) + eps) * weight + bias       (weight None: no output)
+
+    delta_a, delta_b and out are in the run's type (bfloat16 or float32); all arithmetic is 32-bit."""
+    _need(x, torch.float32, "x")
+    hidden = x.shape[-1]
+    given = [t for t in (out, delta_a, delta_b) if t is not None]
+    run = given[0].dtype if given else torch.float32
+    for name, t in (("delta_a", delta_a), ("delta_b", delta_b)):
+        if t is not None:
+            _need(t, run, name)
+            if t.shape != x.shape:
+                raise ValueError(f"residual_layernorm: {name} must have x's shape")
+    for name, t in (("weight", weight), ("bias", bias)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.shape[0] != hidden:
+                raise ValueError(f"residual_layernorm: {name} must have one entry per channel")
+    n_rows = x.shape[0] if rows is None else rows.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    if (weight is None) != (out is None) or (out is not None and (out.shape[0] < n_rows or out.shape[-1] != hidden)):
+        raise ValueError("residual_layernorm: weight and out come together, out [rows, H]")
+    if out is not None:
+        _need(out, run, "out")
+    fn = _fn("elementwise", "lb_residual_layernorm",
+             [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(fn(dtype_code(run), _ptr(x), _ptr(delta_a), _ptr(delta_b), _ptr(weight), _ptr(bias), _ptr(out), _ptr(rows),
+              n_rows, hidden, float(eps), _stream()), "residual_layernorm")
+    return out
+
+
+def heads_bias_rope_kv(proj: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                       q_bias: torch.Tensor | None, k_bias: torch.Tensor | None, v_bias: torch.Tensor | None,
+                       table: torch.Tensor | None, slot_map: torch.Tensor, first_v: torch.Tensor | None, blend: int,
+                       blend_weight: torch.Tensor | None, q_heads: int, kv_heads: int, dim: int, vdim: int,
+                       page_tokens: int) -> None:
+    """Biases, a rotation of the first channels of every q and k head, an optional blend of the values with an
+    earlier layer's, q to q_out and k, v to their pages.
+
+    proj float32 [T, >= q_heads*dim + kv_heads*(dim + vdim)] (rows may be wider); q_out [T, q_heads*R]; k_pool
+    [pages, kv_heads, page_tokens, R]; v_pool likewise (R: each tensor's own room per head, zero-filled beyond the
+    head's channels); biases float32 per channel or None; table float32 [T, 2, n_freq] from `rope_table` (channels i
+    and i + n_freq turn, i < n_freq; None: no rotation); first_v float32 [T, kv_heads*vdim]: `blend` 1 writes this
+    layer's values there, `blend` 2 stores (1 - w) v + w first_v with w = blend_weight (a float32 scalar on the device)."""
+    _need(proj, torch.float32, "proj"); _need(k_pool, q_out.dtype, "k_pool"); _need(v_pool, q_out.dtype, "v_pool")
+    _need(q_out, None, "q_out"); _need(slot_map, torch.int32, "slot_map")
+    tokens = proj.shape[0]
+    used = q_heads * dim + kv_heads * (dim + vdim)
+    if proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[1] < used or q_out.shape[0] != tokens or q_out.shape[1] % q_heads:
+        raise ValueError("heads_bias_rope_kv: the projection row does not hold these heads")
+    q_room, k_room, v_room = q_out.shape[1] // q_heads, k_pool.shape[-1], v_pool.shape[-1]
+    if tuple(k_pool.shape[1:3]) != (kv_heads, page_tokens) or tuple(v_pool.shape[1:3]) != (kv_heads, page_tokens) \
+            or q_room < dim or k_room < dim or v_room < vdim:
+        raise ValueError("heads_bias_rope_kv: the pools do not match the heads")
+    for name, t, n in (("q_bias", q_bias, q_heads * dim), ("k_bias", k_bias, kv_heads * dim), ("v_bias", v_bias, kv_heads * vdim)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != n:
+                raise ValueError(f"heads_bias_rope_kv: {name} must have {n} entries")
+    n_freq = 0
+    if table is not None:
+        _need(table, torch.float32, "table")
+        if table.dim() != 3 or table.shape[0] != tokens or table.shape[1] != 2 or 2 * table.shape[2] > dim:
+            raise ValueError("heads_bias_rope_kv: the rotary table must be [tokens, 2, n_freq] with 2 n_freq <= dim")
+        n_freq = table.shape[2]
+    if blend not in (0, 1, 2):
+        raise ValueError("heads_bias_rope_kv: blend is 0 (none), 1 (keep these values) or 2 (blend with the kept ones)")
+    if blend:
+        _need(first_v, torch.float32, "first_v")
+        if tuple(first_v.shape) != (tokens, kv_heads * vdim):
+            raise ValueError("heads_bias_rope_kv: first_v must be [tokens, kv_heads * vdim]")
+    if blend == 2:
+        _need(blend_weight, torch.float32, "blend_weight")
+        if blend_weight.numel() != 1:
+            raise ValueError("heads_bias_rope_kv: blend_weight is one number")
+    fn = _fn("elementwise", "lb_heads_bias_rope_kv",
+             [c_int, c_void_p, c_long] + [c_void_p] * 7 + [c_int, c_void_p, c_void_p, c_int, c_void_p] + [c_int] * 9 + [c_void_p])
+    _check(fn(dtype_code(q_out.dtype), _ptr(proj), proj.stride(0), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_bias),
+              _ptr(k_bias), _ptr(v_bias), _ptr(table), n_freq, _ptr(slot_map), _ptr(first_v if blend else None), int(blend),
+              _ptr(blend_weight if blend == 2 else None), tokens, q_heads, kv_heads, dim, vdim, page_tokens, q_room, k_room,
+              v_room, _stream()), "heads_bias_rope_kv")
+
+
+def channel_gate(heads: torch.Tensor, logits: torch.Tensor, out: torch.Tensor, q_heads: int, vdim: int) -> torch.Tensor:
+    """out[t, h*vdim + c] = heads[t, h*R + c] * sigmoid(logits[t, h*vdim + c]): heads [T, q_heads*R] (R >= vdim), logits
+    float32 [T, q_heads*vdim] (a view into wider rows is fine), out [T, q_heads*vdim] of heads' type."""
+    _need(heads, None, "heads"); _need(out, heads.dtype, "out")
+    tokens = heads.shape[0]
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1 or tuple(logits.shape) != (tokens, q_heads * vdim) \
+            or tuple(out.shape) != (tokens, q_heads * vdim) or heads.shape[1] % q_heads or heads.shape[1] // q_heads < vdim:
+        raise ValueError("channel_gate: shapes do not agree")
+    fn = _fn("elementwise", "lb_channel_gate", [c_int, c_void_p, c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(heads.dtype), _ptr(heads), _ptr(logits), logits.stride(0), _ptr(out), tokens, q_heads, vdim,
+              heads.shape[1] // q_heads, _stream()), "channel_gate")
+    return out
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """out = act(x) element by element: "relu2" (relu(z)^2), "gelu_tanh", "silu"; 32-bit arithmetic."""
+    _need(x, None, "x"); _need(out, x.dtype, "out")
+    if kind not in ACTIVATIONS or out.shape != x.shape:
+        raise ValueError(f"activation: unknown kind {kind!r} or shapes that do not agree")
+    fn = _fn("elementwise", "lb_activation", [c_int, c_void_p, c_void_p, c_long, c_int, c_void_p])
+    _check(fn(dtype_code(x.dtype), _ptr(x), _ptr(out), x.numel(), ACTIVATIONS[kind], _stream()), "activation")
+    return out
+
+
+def softcap(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """logits <- cap * tanh(logits / cap) in place (float32)."""
+    _need(logits, torch.float32, "logits")
+    if not cap > 0:
+        raise ValueError("softcap: the cap must be positive")
+    fn = _fn("elementwise", "lb_softcap", [c_void_p, c_long, c_float, c_void_p])
+    _check(fn(_ptr(logits), logits.numel(), float(cap), _stream()), "softcap")
+    return logits
+
+
+# ------------------------------------------------------------------ routed experts
+EXPERT_ACTIVATIONS = {"silu": 0, "relu": 1}
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor, scores: torch.Tensor,
+              shared_w: torch.Tensor | None = None, shared_factor: torch.Tensor | None = None) -> None:
+    """ids[t, k], scores[t, k]: the `top` experts with the largest router logits of token t (ties: the lower index) and
+    sigmoid of those logits. h [T, H] in the run's type; router float32 [experts, H]; logits are 32-bit dot products.
+    `shared_w` float32 [H]: also shared_factor[t] = sigmoid(shared_w . h[t])."""
+    _need(h, None, "h"); _need(router, torch.float32, "router"); _need(ids, torch.int32, "ids"); _need(scores, torch.float32, "scores")
+    tokens, hidden = h.shape
+    experts = router.shape[0]
+    if router.shape[1] != hidden or tuple(ids.shape) != (tokens, top) or tuple(scores.shape) != (tokens, top) or not 0 < top <= experts:
+        raise ValueError("moe_route: shapes do not agree")
+    if shared_w is not None:
+        _need(shared_w, torch.float32, "shared_w"); _need(shared_factor, torch.float32, "shared_factor")
+        if shared_w.numel() != hidden or shared_factor.numel() != tokens:
+            raise ValueError("moe_route: shared_w [H] and shared_factor [T]")
+    fn = _fn("moe", "lb_moe_route", [c_int] + [c_void_p] * 6 + [c_int] * 4 + [c_void_p])
+    _check(fn(dtype_code(h.dtype), _ptr(h), _ptr(router), _ptr(shared_w), _ptr(ids), _ptr(scores), _ptr(shared_factor), tokens,
+              hidden, experts, int(top), _stream()), "moe_route")
+
+
+def moe_group(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor) -> None:
+    """Group the (token, k) pairs by expert: order int32 [pairs] lists the pairs expert by expert, expert e's at places
+    offsets[e] .. offsets[e + 1] (offsets int32 [experts + 1])."""
+    _need(ids, torch.int32, "ids"); _need(offsets, torch.int32, "offsets"); _need(order, torch.int32, "order")
+    if offsets.numel() != experts + 1 or order.numel() != ids.numel():
+        raise ValueError("moe_group: offsets [experts + 1], order one entry per pair")
+    fn = _fn("moe", "lb_moe_group", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(ids), ids.numel(), int(experts), _ptr(offsets), _ptr(order), _stream()), "moe_group")
+
+
+def moe_expert_up(h: torch.Tensor, order: torch.Tensor, offsets: torch.Tensor, scores: torch.Tensor | None,
+                  gate_up: torch.Tensor, act: torch.Tensor, top: int, activation: str = "silu") -> torch.Tensor:
+    """act[place] = act_fn(s * gate_e h[token]) * (s * up_e h[token]) for every place of `order` (pair = token * top + k, s =
+    scores[pair] or 1): gate_up [experts, 2 * inter, H] (gate rows, then up rows), act [pairs, inter] in the run's type."""
+    _need(h, None, "h"); _need(gate_up, h.dtype, "gate_up"); _need(act, h.dtype, "act")
+    experts, two_inter, hidden = gate_up.shape
+    pairs = order.numel()
+    if hidden != h.shape[1] or two_inter % 2 or tuple(act.shape) != (pairs, two_inter // 2) or pairs != h.shape[0] * top \
+            or activation not in EXPERT_ACTIVATIONS:
+        raise ValueError("moe_expert_up: shapes do not agree")
+    fn = _fn("moe", "lb_moe_expert_up", [c_int, c_void_p, c_long] + [c_void_p] * 5 + [c_int] * 6 + [c_void_p])
+    _check(fn(dtype_code(h.dtype), _ptr(h), h.stride(0), _ptr(order), _ptr(offsets), _ptr(scores), _ptr(gate_up), _ptr(act),
+              pairs, int(top), experts, hidden, two_inter // 2, EXPERT_ACTIVATIONS[activation], _stream()), "moe_expert_up")
+    return act
+
+
+def moe_expert_down(act: torch.Tensor, order: torch.Tensor, offsets: torch.Tensor, down: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """y[pair] = down_e act[place] in 32-bit: down [experts, H, inter], y float32 [pairs, H] indexed by pair."""
+    _need(act, None, "act"); _need(down, act.dtype, "down"); _need(y, torch.float32, "y")
+    experts, hidden, inter = down.shape
+    pairs = order.numel()
+    if tuple(act.shape) != (pairs, inter) or tuple(y.shape) != (pairs, hidden):
+        raise ValueError("moe_expert_down: shapes do not agree")
+    fn = _fn("moe", "lb_moe_expert_down", [c_int] + [c_void_p] * 5 + [c_int] * 4 + [c_void_p])
+    _check(fn(dtype_code(act.dtype), _ptr(act), _ptr(order), _ptr(offsets), _ptr(down), _ptr(y), pairs, experts, hidden, inter,
+              _stream()), "moe_expert_down")
+    return y
+
+
+def moe_combine(y: torch.Tensor, out: torch.Tensor, top: int, pair_scale: torch.Tensor | None = None,
+                shared_out: torch.Tensor | None = None, shared_factor: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = sum_k c_k y[t * top + k] + f_t shared_out[t], c = pair_scale or 1, f = shared_factor or 1; y float32
+    [T * top, H], out and shared_out [T, H] in the run's type."""
+    _need(y, torch.float32, "y"); _need(out, None, "out")
+    tokens, hidden = out.shape
+    if tuple(y.shape) != (tokens * top, hidden):
+        raise ValueError("moe_combine: y must be [tokens * top, H]")
+    if shared_out is not None:
+        _need(shared_out, out.dtype, "shared_out")
+        if shared_out.shape != out.shape:
+            raise ValueError("moe_combine: shared_out must have out's shape")
+    for name, t in (("pair_scale", pair_scale), ("shared_factor", shared_factor)):
+        if t is not None:
+            _need(t, torch.float32, name)
+    fn = _fn("moe", "lb_moe_combine", [c_int] + [c_void_p] * 5 + [c_int] * 3 + [c_void_p])
+    _check(fn(dtype_code(out.dtype), _ptr(y), _ptr(pair_scale), _ptr(shared_out), _ptr(shared_factor), _ptr(out), tokens, hidden,
+              int(top), _stream()), "moe_combine")
+    return out
+
+
 # ------------------------------------------------------------------ linear attention (a recurrence over state slots)
 SCAN_ACTIVATIONS = {None: 0, "none": 0, "silu": 1}
 
@@ -382,13 +592,14 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
                    block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, tile_seq: torch.Tensor,
                    tile_q0: torch.Tensor, n_tiles: int, q_heads: int, kv_heads: int, dim: int, page_tokens: int,
                    scale: float, window: int = 0, vdim: int | None = None, sinks: torch.Tensor | None = None,
-                   gates: torch.Tensor | None = None) -> torch.Tensor:
+                   gates: torch.Tensor | None = None, chunk: int = 0) -> torch.Tensor:
     """Paged causal attention in 32-bit arithmetic for any mix of segment lengths.
 
     q [T, q_heads * dim]; out [T, q_heads * vdim] (vdim defaults to dim); pools [pages, kv_heads, page_tokens,
     dim or vdim]; block_table int32 [S, W]; cu_q int32 [S + 1]; ctx_len int32 [S]; (tile_seq, tile_q0) int32
     [n_tiles] list the query tiles. `sinks` float32 [q_heads]: a score per head that joins the softmax's
-    denominator only; `gates` float32 [T, q_heads]: a factor on each head's output."""
+    denominator only; `gates` float32 [T, q_heads]: a factor on each head's output. `chunk` > 0: a query sees
+    only the keys of its own chunk of that many positions (counted from position 0 of its sequence)."""
     vdim = dim if vdim is None else int(vdim)
     _need(q, None, "q"); _need(out, q.dtype, "out"); _need(k_pool, q.dtype, "k_pool"); _need(v_pool, q.dtype, "v_pool")
     if tuple(out.shape) != (q.shape[0], q_heads * vdim) or k_pool.shape[-1] != dim or v_pool.shape[-1] != vdim:
@@ -406,21 +617,21 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
         _need(t, torch.int32, name)
     fn = _fn("attention_simt", "lb_attention_simt",
              [c_int] + [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int] * 5 + [c_float, c_int, c_int, c_void_p,
-                                                                                c_void_p, c_void_p])
+                                                                                c_void_p, c_int, c_void_p])
     _check(fn(dtype_code(q.dtype), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
               block_table.shape[1], _ptr(cu_q), _ptr(ctx_len), _ptr(tile_seq), _ptr(tile_q0), n_tiles, q_heads,
-              kv_heads, dim, page_tokens, float(scale), int(window), vdim, _ptr(sinks), _ptr(gates), _stream()),
+              kv_heads, dim, page_tokens, float(scale), int(window), vdim, _ptr(sinks), _ptr(gates), int(chunk), _stream()),
            "attention_simt")
     return out
 
 
 def attention_f32(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window, vdim=None,
-                  sinks=None, gates=None):
+                  sinks=None, gates=None, chunk=0):
     """The 32-bit path's attention for one step: one kernel for every mix of segment lengths (and, in
     either precision, the attention with sinks, head gates or values of another size than keys)."""
     tiles = batch.tiles[attention_simt_block_queries()]
     attention_simt(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq, tiles.tile_q0,
-                   tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates)
+                   tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates, chunk)
 
 
 # ------------------------------------------------------------------ sampling
@@ -678,6 +889,7 @@ def _sink_arguments(sinks, gates, tokens, q_heads, what):
 def attention_prefill_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, tile_seq, tile_q0, n_tiles, q_heads,
                            kv_heads, dim, page_tokens, scale, window=0, sinks=None, gates=None, exact_weights=False):
     """Tensor-core paged attention for prompt portions: tiles of 64 queries, any number of queries per sequence.
+    `window` > 0: the last `window` keys; `window` < 0: a chunked mask, the keys of the query's own chunk of -window positions.
     `sinks` float32 [q_heads] join the softmax's denominator only, `gates` float32 [T, q_heads] multiply the
     heads' outputs, `exact_weights` keeps 16 bits of the weights' mantissa in the second product."""
     _sink_arguments(sinks, gates, q.shape[0], q_heads, "attention_prefill_bf16")
@@ -841,15 +1053,19 @@ def attention_tcgen05_prefill(q, pool, layer, out, block_table, cu_q, ctx_len, t
 
 
 def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window, sinks=None,
-                   gates=None, exact_weights=False):
+                   gates=None, exact_weights=False, chunk=0):
     """The bfloat16 path's attention for one step: prompt portions go through the tcgen05 tile kernel
     where it takes the sizes (head size 128, pages of 8..128 tokens), else through the mma.sync
     one; single tokens, alone or beside prompt portions, go through the split decode kernel. With
     sinks, gates or exact weights the mma.sync kernels' variants for those run everywhere."""
-    plain = sinks is None and gates is None and not exact_weights
+    plain = sinks is None and gates is None and not exact_weights and not chunk
     extras = dict(sinks=sinks, gates=gates, exact_weights=exact_weights)
-    # a window bounds the keys a single token reads, whatever its request's length
-    seen = (lambda ctx: min(ctx, window + 63)) if window else (lambda ctx: ctx)
+    if chunk:
+        if window:
+            raise ValueError("attention_bf16: a window and a chunked mask do not combine")
+        window = -int(chunk)      # the mma.sync kernels read a negative window as a chunked mask of that size
+    # a window (or a chunk) bounds the keys a single token reads, whatever its request's length
+    seen = (lambda ctx: min(ctx, abs(window) + 63)) if window else (lambda ctx: ctx)
     if batch.all_decode and q_heads // kv_heads <= 16:
         sms = gemm_scratch(q.device)[2]
         # planned for the step's own lengths; a captured step for its class of steps (the widest context

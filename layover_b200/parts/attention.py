@@ -45,7 +45,19 @@ class Attention(Part):
     the split kernel for single tokens) in their variant whose weights enter the second product with
     16 bits of mantissa, where the head sizes are multiples of 16 (keys and values of different
     sizes then share pages of the larger size, zero-filled: zeros change no score and no sum), and
-    the 32-bit kernel on bfloat16 pages otherwise. That path has no rotation and no shared cache."""
+    the 32-bit kernel on bfloat16 pages otherwise. That path has no shared cache.
+
+    More options of the general path: `q_bias`, `k_bias`, `v_bias` (tensor names: a bias per channel of a
+    projection, added before anything else); a `position` whose table rotates only the first channels of a
+    head; `chunk` (a chunked mask: position i sees j <= i only where floor(i / chunk) == floor(j / chunk),
+    chunks counted from position 0 of the sequence; the cache gives back the pages of finished chunks);
+    `gate_kind` = "channel" (`gate` is then a [q_heads * v_head_dim, hidden] matrix and every channel of
+    the concatenated heads is multiplied by its own sigmoid; default "head"); `value_blend` = "keep" (this
+    layer's values, bias included, are kept for the rest of the step) or "blend" (the values that go to the
+    cache are (1 - w) v + w kept values of the same token, w = the scalar tensor `value_blend_weight`).
+    With any of these the stacked product leaves 32-bit rows and ONE kernel adds the biases, rotates, blends
+    and writes q and the pages (rounded once); a channel gate is one more small kernel after the attention.
+    They do not combine with the whole-row norm or head gates."""
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -58,7 +70,18 @@ class Attention(Part):
         self.qk_norm = p.get("qk_norm", "per_head")
         if self.qk_norm not in ("per_head", "whole"):
             raise ValueError(f"qk_norm must be 'per_head' or 'whole', got {self.qk_norm!r}")
-        self.general = bool(self.vdim != self.dim or self.qk_norm == "whole" or p.get("sink") or p.get("gate"))
+        self.biases = [k for k in ("q_bias", "k_bias", "v_bias") if p.get(k)]
+        self.chunk = int(p.get("chunk") or 0)
+        self.gate_kind = p.get("gate_kind", "head")
+        self.value_blend = p.get("value_blend")
+        if self.gate_kind not in ("head", "channel") or self.value_blend not in (None, "keep", "blend"):
+            raise ValueError("attention: gate_kind is 'head' or 'channel', value_blend None, 'keep' or 'blend'")
+        position = p.get("position")
+        partial = bool(position and int(position.params.get("rotated") or p["head_dim"]) != int(p["head_dim"]))
+        # biases, a partial rotation, a blend of values or a gate per channel: one kernel over 32-bit projection rows
+        self.rows32 = bool(self.biases or partial or self.value_blend or (p.get("gate") and self.gate_kind == "channel")
+                           or (position and (p.get("v_head_dim") or p["head_dim"]) != p["head_dim"]) or self.chunk)
+        self.general = bool(self.vdim != self.dim or self.qk_norm == "whole" or p.get("sink") or p.get("gate") or self.rows32)
         if self.general:
             if self.dim % 4 or self.vdim % 4:
                 raise ValueError(f"head sizes must be multiples of 4, got {self.dim} and {self.vdim}")
@@ -71,13 +94,22 @@ class Attention(Part):
         self.shares_cache = bool(p.get("shares_cache", False))
         self.scale = float(p.get("scale") or 1.0 / math.sqrt(self.dim))
         self.position = build_part("position", p.get("position"), prefix)
-        if self.general and (self.shares_cache or self.position is not None):
-            raise ValueError("attention with sinks, gates, a whole-row norm or its own value size has no rotation "
+        if self.general and (self.shares_cache or (self.position is not None and not self.rows32)):
+            raise ValueError("attention with sinks, head gates, a whole-row norm or its own value size has no rotation "
                              "and no shared cache")
+        if self.rows32 and (self.qk_norm_eps is not None or (p.get("gate") and self.gate_kind == "head")):
+            raise ValueError("attention: biases, partial rotation, chunks, value blends and channel gates do not combine "
+                             "with q/k norms or head gates")
+        if self.chunk and self.window:
+            raise ValueError("attention: a window and a chunked mask do not combine")
+        if self.chunk < 0:
+            raise ValueError("attention: chunk must be positive")
         wanted = ["q", "o"] + ([] if self.shares_cache else ["k", "v"])
         if self.qk_norm_eps is not None:
             wanted += ["q_norm"] + ([] if self.shares_cache else ["k_norm"])
-        wanted += [k for k in ("sink", "gate") if p.get(k)]
+        wanted += [k for k in ("sink", "gate") if p.get(k)] + self.biases
+        if self.value_blend == "blend":
+            wanted.append("value_blend_weight")
         self.require(*wanted)
         self.names = {k: prefix + p[k] for k in wanted}
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = self.sink = None
@@ -101,15 +133,20 @@ class Attention(Part):
         if "sink" in n:
             specs.append(TensorSpec(n["sink"], (self.q_heads,), kind="vector"))
         if "gate" in n:
-            specs.append(TensorSpec(n["gate"], (self.q_heads, self.hidden)))
+            specs.append(TensorSpec(n["gate"], (self.q_heads * (self.vdim if self.gate_kind == "channel" else 1), self.hidden)))
+        sizes = {"q_bias": self.q_heads * self.dim, "k_bias": self.kv_heads * self.dim, "v_bias": self.kv_heads * self.vdim}
+        specs += [TensorSpec(n[k], (sizes[k],), kind="vector", init="zeros") for k in self.biases]
+        if self.value_blend == "blend":
+            specs.append(TensorSpec(n["value_blend_weight"], (), kind="vector", init="zeros"))
         if self.position is not None:
             specs += self.position.tensor_specs()
         return specs
 
     def cache_need(self):
+        chunk = self.chunk or None
         if self.room is not None:
-            return PagedKVNeed(self.kv_heads, self.room, self.window)
-        return PagedKVNeed(self.kv_heads, self.dim, self.window, self.vdim if self.vdim != self.dim else None)
+            return PagedKVNeed(self.kv_heads, self.room, self.window, chunk=chunk)
+        return PagedKVNeed(self.kv_heads, self.dim, self.window, self.vdim if self.vdim != self.dim else None, chunk=chunk)
 
     def _on_tensor_cores(self, dtype) -> bool:
         """Whether the general path runs on the tensor-core kernels in a run of `dtype`."""
@@ -173,30 +210,62 @@ class Attention(Part):
         if self.qk_norm_eps is not None:
             self.q_norm_w, self.k_norm_w = tensors[n["q_norm"]], tensors[n["k_norm"]]
         self.sink = tensors[n["sink"]] if "sink" in n else None
+        self.bias = {k: tensors[n[k]] for k in self.biases}
+        self.blend_weight = tensors[n["value_blend_weight"]].reshape(1) if self.value_blend == "blend" else None
+        if self.position is not None:
+            self.position.bind(tensors, runtime)
         if self._on_tensor_cores(runtime.dtype):
             ops.attention_scratch(runtime.device)      # made now, never inside a graph capture
             self.room = max(self.dim, self.vdim)
-            if self.room != self.vdim:                 # the heads' outputs arrive padded: zero columns in the output matrix
+            # the heads' outputs arrive padded: zero columns in the output matrix (a channel gate writes them dense)
+            if self.room != self.vdim and not ("gate" in n and self.gate_kind == "channel"):
                 wide = torch.zeros((self.hidden, self.q_heads, self.room), dtype=self.w_o.dtype, device=self.w_o.device)
                 wide[:, :, : self.vdim] = self.w_o.view(self.hidden, self.q_heads, self.vdim)
                 self.w_o = wide.view(self.hidden, self.q_heads * self.room).contiguous()
 
+    def _kept_values(self, batch, tokens, device):
+        """The step's buffer of kept values [T, kv_heads * v_head_dim], 32-bit: made by the layer that keeps,
+        found by the layers that blend (`batch.shared` lives for one step)."""
+        key = ("value_blend", self.kv_heads, self.vdim)
+        if self.value_blend == "keep":
+            batch.shared[key] = torch.empty((tokens, self.kv_heads * self.vdim), dtype=torch.float32, device=device)
+        elif key not in batch.shared:
+            raise ValueError("attention: a layer blends its values before any layer of the model kept them")
+        return batch.shared[key]
+
     def _forward_general(self, h, batch, cache):
         tokens, group = h.shape[0], batch.groups[cache.group]
-        proj = self.runtime.linear(h, self.w_qkv)
         room = self.room or self.dim
         q = torch.empty((tokens, self.q_heads * room), dtype=h.dtype, device=h.device)
-        gates = torch.empty((tokens, self.q_heads), dtype=torch.float32, device=h.device) if "gate" in self.names else None
-        ops.qk_rownorm_kv(proj, q, cache.k_pool, cache.v_pool, self.q_norm_w, self.k_norm_w, group.slot_map, gates,
-                          self.q_heads, self.kv_heads, self.dim, self.vdim, cache.page_tokens, float(self.qk_norm_eps or 0.0))
+        gates = None
+        if self.rows32:
+            proj = self.runtime.linear(h, self.w_qkv, out_dtype=torch.float32)
+            table = self.position.tables(batch) if self.position is not None else None
+            if self.position is not None and table is None:
+                raise ValueError("attention: this position encoding offers no table for the fused kernel")
+            blend = {None: 0, "keep": 1, "blend": 2}[self.value_blend]
+            kept = self._kept_values(batch, tokens, h.device) if blend else None
+            ops.heads_bias_rope_kv(proj, q, cache.k_pool, cache.v_pool, self.bias.get("q_bias"), self.bias.get("k_bias"),
+                                   self.bias.get("v_bias"), table, group.slot_map, kept, blend, self.blend_weight,
+                                   self.q_heads, self.kv_heads, self.dim, self.vdim, cache.page_tokens)
+        else:
+            proj = self.runtime.linear(h, self.w_qkv)
+            if "gate" in self.names:
+                gates = torch.empty((tokens, self.q_heads), dtype=torch.float32, device=h.device)
+            ops.qk_rownorm_kv(proj, q, cache.k_pool, cache.v_pool, self.q_norm_w, self.k_norm_w, group.slot_map, gates,
+                              self.q_heads, self.kv_heads, self.dim, self.vdim, cache.page_tokens, float(self.qk_norm_eps or 0.0))
         if self.room is not None:
             out = torch.empty((tokens, self.q_heads * room), dtype=h.dtype, device=h.device)
             ops.attention_bf16(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, room, cache.page_tokens,
-                               self.scale, self.window or 0, sinks=self.sink, gates=gates, exact_weights=True)
+                               self.scale, self.window or 0, sinks=self.sink, gates=gates, exact_weights=True, chunk=self.chunk)
         else:
             out = torch.empty((tokens, self.q_heads * self.vdim), dtype=h.dtype, device=h.device)
             ops.attention_f32(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.dim, cache.page_tokens,
-                              self.scale, self.window or 0, self.vdim, self.sink, gates)
+                              self.scale, self.window or 0, self.vdim, self.sink, gates, chunk=self.chunk)
+        if self.rows32 and "gate" in self.names:
+            at = self.q_heads * self.dim + self.kv_heads * (self.dim + self.vdim)
+            gated = torch.empty((tokens, self.q_heads * self.vdim), dtype=h.dtype, device=h.device)
+            out = ops.channel_gate(out, proj[:, at: at + self.q_heads * self.vdim], gated, self.q_heads, self.vdim)
         return self.runtime.linear(out, self.w_o)
 
     # ---- one step

@@ -52,11 +52,14 @@ class PartSpec:
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values of every token (window None) or of the last `window` tokens, in pages.
-    `v_head_dim`: the size of a value where it differs from a key's (None: the same)."""
+    `v_head_dim`: the size of a value where it differs from a key's (None: the same).
+    `chunk`: a query only sees keys of its own chunk of that many positions (counted from 0), so the
+    pages of finished chunks are never read again."""
     kv_heads: int
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None
+    chunk: int | None = None
 
     @property
     def value_dim(self) -> int:

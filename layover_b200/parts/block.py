@@ -105,3 +105,44 @@ class SandwichNormBlock(Part):
         with profiling.nvtx_range("feed_forward") if profiling.active() else _NO_RANGE:
             h = self.post_norm.forward(x, mixed)
             return x, self.ff_out_norm.defer(self.feed_forward.forward(h))
+
+
+@register_block("parallel")
+class ParallelBlock(Part):
+    """One norm, and both sub-layers read its output: h = norm(x); x = x + (mixer(h) + feed_forward(h)).
+
+    Nothing is added here: the two outputs are handed on as a pair and the next norm of the stream
+    (the next block's, or the model's final one) adds them, x + (a + b), in the kernel that norms the
+    sum. A layer without a feed-forward hands on (a, None).
+
+    params: input_norm, mixer (PartSpecs); feed_forward (a PartSpec or None)."""
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.require("input_norm", "mixer")
+        self.input_norm = build_part("norm", params["input_norm"], prefix)
+        self.mixer = build_part("mixer", params["mixer"], prefix)
+        self.feed_forward = build_part("feed_forward", params.get("feed_forward"), prefix)
+
+    def parts(self):
+        return [p for p in (self.input_norm, self.mixer, self.feed_forward) if p is not None]
+
+    def tensor_specs(self):
+        return [spec for part in self.parts() for spec in part.tensor_specs()]
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        for part in self.parts():
+            part.bind(tensors, runtime)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, x, delta, batch, cache, extra=None):
+        h = self.input_norm.forward(x, delta, extra=extra)
+        with profiling.nvtx_range("mixer") if profiling.active() else _NO_RANGE:
+            mixed = self.mixer.forward(h, batch, cache)
+        if self.feed_forward is None:
+            return x, (mixed, None)
+        with profiling.nvtx_range("feed_forward") if profiling.active() else _NO_RANGE:
+            return x, (mixed, self.feed_forward.forward(h))

@@ -6,7 +6,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import Part, register_feed_forward
+from .base import Part, build_part, register_feed_forward
 
 
 @register_feed_forward("gated_mlp")
@@ -73,3 +73,124 @@ class GatedMLP(Part):
         else:
             ops.gated_act(gate_up, act, self.activation)
         return self.runtime.linear(act, self.down)
+
+
+@register_feed_forward("mlp")
+class MLP(Part):
+    """down(act(up(x))) without gate and without bias; act = "relu2" (the square of relu), "gelu_tanh" or "silu".
+
+    params: hidden, inter, activation (default "relu2"), up, down (tensor names relative to the prefix)."""
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.require("hidden", "inter", "up", "down")
+        self.hidden, self.inter = int(params["hidden"]), int(params["inter"])
+        self.activation = params.get("activation", "relu2")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"mlp: unsupported activation {self.activation!r}")
+        self.names = {k: prefix + params[k] for k in ("up", "down")}
+        self.up = self.down = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.names["up"], (self.inter, self.hidden)),
+                TensorSpec(self.names["down"], (self.hidden, self.inter))]
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        self.up, self.down = tensors[self.names["up"]], tensors[self.names["down"]]
+
+    def kernel_libraries(self, dtype):
+        return ("elementwise",)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        up = self.runtime.linear(h, self.up)
+        return self.runtime.linear(ops.activation(up, up, self.activation), self.down)
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(Part):
+    """A mixture of small gated feed-forwards: every token goes to the `top` experts with the largest router
+    scores and their outputs are added; optionally a shared expert that every token uses is added too.
+
+        z = router h (32-bit), s = sigmoid(z); chosen = the `top` largest; no renormalisation of the chosen scores
+        out = sum over chosen e of expert_e(s_e h) + sigmoid(shared_gate . h) * shared(h)
+        expert(x) = down(act(gate x) * (up x)), act = silu (or relu)
+
+    The score scales the expert's INPUT (`weight_on` = "input", the only form built). On the device:
+    route (one warp per token) -> group the (token, expert) pairs by expert -> one launch for all experts'
+    gate/up products with the activation in its epilogue -> one for their down products -> the sum over a
+    token's experts with the shared expert in the same kernel. Nothing comes back to the host in between,
+    so a step with routed layers is captured in a CUDA graph like any other.
+
+    params: hidden, experts, top, inter, activation ("silu"), router (tensor name), expert_gate / expert_up /
+    expert_down (tensor names with `{}` for the expert's index), shared (a feed-forward PartSpec or None),
+    shared_gate (tensor name of a [1, hidden] matrix, or None: the shared expert is added as it is)."""
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.require("hidden", "experts", "top", "inter", "router", "expert_gate", "expert_up", "expert_down")
+        p = params
+        self.hidden, self.experts, self.top, self.inter = (int(p[k]) for k in ("hidden", "experts", "top", "inter"))
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"routed_experts: top ({self.top}) must lie in 1..experts ({self.experts})")
+        self.activation = p.get("activation", "silu")
+        if self.activation not in ops.EXPERT_ACTIVATIONS:
+            raise ValueError(f"routed_experts: unsupported activation {self.activation!r}")
+        if p.get("weight_on", "input") != "input" or p.get("score", "sigmoid") != "sigmoid" or p.get("renormalize", False):
+            raise ValueError("routed_experts: built for sigmoid scores that scale the expert's input, not renormalised")
+        self.router_name = prefix + p["router"]
+        self.expert_names = [{k: prefix + p["expert_" + k].format(e) for k in ("gate", "up", "down")} for e in range(self.experts)]
+        self.shared = build_part("feed_forward", p.get("shared"), prefix)
+        self.shared_gate_name = prefix + p["shared_gate"] if p.get("shared_gate") else None
+        if self.shared_gate_name and self.shared is None:
+            raise ValueError("routed_experts: a shared gate without a shared expert")
+        self.router = self.gate_up = self.down = self.shared_gate = None
+
+    def parts(self):
+        return [self.shared] if self.shared is not None else []
+
+    def tensor_specs(self):
+        specs = [TensorSpec(self.router_name, (self.experts, self.hidden), kind="keep32")]
+        for names in self.expert_names:
+            specs += [TensorSpec(names["gate"], (self.inter, self.hidden)), TensorSpec(names["up"], (self.inter, self.hidden)),
+                      TensorSpec(names["down"], (self.hidden, self.inter))]
+        if self.shared is not None:
+            specs += self.shared.tensor_specs()
+        if self.shared_gate_name:
+            specs.append(TensorSpec(self.shared_gate_name, (1, self.hidden), kind="keep32"))
+        return specs
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        self.router = tensors[self.router_name]
+        self.gate_up = torch.stack([torch.cat((tensors.pop(n["gate"]), tensors.pop(n["up"])), dim=0) for n in self.expert_names]).contiguous()
+        self.down = torch.stack([tensors.pop(n["down"]) for n in self.expert_names]).contiguous()
+        if self.shared is not None:
+            self.shared.bind(tensors, runtime)
+        self.shared_gate = tensors[self.shared_gate_name].reshape(-1).contiguous() if self.shared_gate_name else None
+
+    def kernel_libraries(self, dtype):
+        return ("elementwise", "moe")
+
+    def route(self, h: torch.Tensor):
+        """(expert ids [T, top] int32, their scores [T, top] float32, the shared expert's factor [T] or None)."""
+        tokens = h.shape[0]
+        ids = torch.empty((tokens, self.top), dtype=torch.int32, device=h.device)
+        scores = torch.empty((tokens, self.top), dtype=torch.float32, device=h.device)
+        factor = torch.empty((tokens,), dtype=torch.float32, device=h.device) if self.shared_gate is not None else None
+        ops.moe_route(h, self.router, self.top, ids, scores, self.shared_gate, factor)
+        return ids, scores, factor
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        tokens, pairs = h.shape[0], h.shape[0] * self.top
+        ids, scores, factor = self.route(h)
+        offsets = torch.empty((self.experts + 1,), dtype=torch.int32, device=h.device)
+        order = torch.empty((pairs,), dtype=torch.int32, device=h.device)
+        ops.moe_group(ids, self.experts, offsets, order)
+        act = torch.empty((pairs, self.inter), dtype=h.dtype, device=h.device)
+        ops.moe_expert_up(h, order, offsets, scores, self.gate_up, act, self.top, self.activation)
+        y = torch.empty((pairs, self.hidden), dtype=torch.float32, device=h.device)
+        ops.moe_expert_down(act, order, offsets, self.down, y)
+        shared = self.shared.forward(h) if self.shared is not None else None
+        out = torch.empty((tokens, self.hidden), dtype=h.dtype, device=h.device)
+        return ops.moe_combine(y, out, self.top, None, shared, factor)

@@ -1,4 +1,4 @@
-"""RMSNorm, fused with the residual addition that precedes it."""
+"""RMSNorm and LayerNorm, each fused with the residual addition that precedes it."""
 
 from __future__ import annotations
 
@@ -74,4 +74,66 @@ class RMSNorm(Part):
         value, weight, eps = (delta.value, delta.weight, delta.eps) if isinstance(delta, Deferred) else (delta, None, 0.0)
         if value is not None or extra is not None:
             ops.residual_rmsnorm(x, value, weight, eps, extra, None, 0.0, None)
+        return x
+
+
+@register_norm("layernorm")
+class LayerNorm(Part):
+    """y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * weight + bias over a 32-bit residual stream.
+
+    params: dim, eps, weight, bias (tensor names relative to the prefix; bias may be None).
+    `forward(x, delta)` first adds what has not joined the stream yet: `delta` is None, one tensor, or a
+    pair of tensors (the two sub-layers of a parallel block, either of which may be None), added as
+    x + (a + b) in 32-bit in the same kernel as the norm. The stream must be float32 (a model with
+    `residual_dtype="float32"`); the output is in the run's type, rounded once."""
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.require("dim", "eps", "weight")
+        self.dim, self.eps = int(params["dim"]), float(params["eps"])
+        self.weight_name = prefix + params["weight"]
+        self.bias_name = prefix + params["bias"] if params.get("bias") else None
+        self.weight = self.bias = None
+
+    def tensor_specs(self):
+        specs = [TensorSpec(self.weight_name, (self.dim,), kind="vector", init="ones")]
+        if self.bias_name:
+            specs.append(TensorSpec(self.bias_name, (self.dim,), kind="vector", init="zeros"))
+        return specs
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        self.weight = tensors[self.weight_name]
+        self.bias = tensors[self.bias_name] if self.bias_name else None
+
+    def kernel_libraries(self, dtype):
+        return ("elementwise",)
+
+    @staticmethod
+    def _pair(delta):
+        if isinstance(delta, Deferred):
+            raise ValueError("layernorm: a sub-layer output that is normed before it is added needs an RMSNorm after it")
+        if isinstance(delta, (tuple, list)):
+            if len(delta) != 2:
+                raise ValueError("layernorm adds at most two pending outputs at once")
+            return delta[0], delta[1]
+        return delta, None
+
+    def forward(self, x: torch.Tensor, delta, rows: torch.Tensor | None = None,
+                extra: torch.Tensor | None = None) -> torch.Tensor:
+        if x.dtype != torch.float32:
+            raise ValueError("layernorm runs over a 32-bit residual stream")
+        if extra is not None:
+            raise ValueError("layernorm takes no extra summand")
+        first, second = self._pair(delta)
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, self.dim), dtype=self.runtime.dtype, device=x.device)
+        return ops.residual_layernorm(x, first, second, self.weight, self.bias, self.eps, out, rows)
+
+    @classmethod
+    def add(cls, x: torch.Tensor, delta, extra: torch.Tensor | None = None) -> torch.Tensor:
+        """x += the pending outputs, no norm: the stream itself."""
+        first, second = cls._pair(delta)
+        if first is not None or second is not None:
+            ops.residual_layernorm(x, first, second, None, None, 0.0, None)
         return x

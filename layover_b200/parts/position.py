@@ -19,20 +19,32 @@ class RotaryHalf(Part):
     tables once per call, layover/model.py:220-221); the rotation itself runs inside the mixer's
     fused kernel.
 
-    params: dim (the head's size), theta."""
+    params: dim (the head's size), theta; optional `rotated` (only the first `rotated` channels of a head
+    turn, channel i paired with channel i + rotated/2, frequencies theta^(-2i/rotated); default: the whole
+    head) and `linear_factor` (every frequency is divided by it: positions are read on a coarser scale;
+    default 1). With either, the frequencies are made in float64 and rounded once to 32-bit."""
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
         self.require("dim", "theta")
         self.dim, self.theta = int(params["dim"]), float(params["theta"])
-        if self.dim % 2:
-            raise ValueError("rotary_half needs an even head size")
+        self.rotated = int(params.get("rotated") or self.dim)
+        self.linear_factor = float(params.get("linear_factor") or 1.0)
+        if self.rotated % 2 or not 0 < self.rotated <= self.dim:
+            raise ValueError(f"rotary_half rotates an even number of channels up to the head size, got {self.rotated} of {self.dim}")
+        if not self.linear_factor > 0:
+            raise ValueError("rotary_half: linear_factor must be positive")
         self._table = None
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
-        exponent = torch.arange(0, self.dim, 2, dtype=torch.float32) / self.dim
-        self._table = (1.0 / (self.theta ** exponent)).to(runtime.device).contiguous()
+        if self.rotated == self.dim and self.linear_factor == 1.0:
+            exponent = torch.arange(0, self.dim, 2, dtype=torch.float32) / self.dim
+            self._table = (1.0 / (self.theta ** exponent)).to(runtime.device).contiguous()
+        else:
+            exponent = torch.arange(0, self.rotated, 2, dtype=torch.float64) / self.rotated
+            freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -exponent) / self.linear_factor
+            self._table = freq.to(torch.float32).to(runtime.device).contiguous()
 
     def kernel_libraries(self, dtype):
         return ("elementwise",)
@@ -42,10 +54,10 @@ class RotaryHalf(Part):
 
     def tables(self, batch) -> torch.Tensor | None:
         """The step's cos/sin table for the fused kernel; parts that cannot be fused return None."""
-        key = ("rotary_half", self.dim, self.theta)
+        key = ("rotary_half", self.dim, self.theta, self.rotated, self.linear_factor)
         table = batch.shared.get(key)
         if table is None:
-            table = torch.empty((batch.n_tokens, 2, self.dim // 2), dtype=torch.float32, device=self._table.device)
+            table = torch.empty((batch.n_tokens, 2, self.rotated // 2), dtype=torch.float32, device=self._table.device)
             ops.rope_table(batch.positions, self._table, table)
             batch.shared[key] = table
         return table
