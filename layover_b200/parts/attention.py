@@ -83,7 +83,7 @@ class Attention(Part):
                            or (position and (p.get("v_head_dim") or p["head_dim"]) != p["head_dim"]) or self.chunk)
         self.general = bool(self.vdim != self.dim or self.qk_norm == "whole" or p.get("sink") or p.get("gate") or self.rows32)
         if self.general:
-            if self.dim % 4 or self.vdim % 4:
+            if (self.dim % 4 or self.vdim % 4) and not self.rows32:
                 raise ValueError(f"head sizes must be multiples of 4, got {self.dim} and {self.vdim}")
         elif self.dim % 16:
             raise ValueError(f"head_dim must be a multiple of 16, got {self.dim}")
@@ -115,6 +115,9 @@ class Attention(Part):
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = self.sink = None
         self._attend = self._project_heads = None
         self.room = None        # once bound: the size keys, values and queries are padded to for the tensor-core kernels
+        # where the tensor-core kernels do not run: the room of a key and of a value in their pages (the 32-bit kernel
+        # reads four channels at a time; the kernel over 32-bit projection rows fills the rest of the room with zeros)
+        self.k_room, self.v_room = (-(-self.dim // 4) * 4, -(-self.vdim // 4) * 4) if self.rows32 else (self.dim, self.vdim)
 
     # ---- what it wants
     def tensor_specs(self):
@@ -135,9 +138,9 @@ class Attention(Part):
         if "gate" in n:
             specs.append(TensorSpec(n["gate"], (self.q_heads * (self.vdim if self.gate_kind == "channel" else 1), self.hidden)))
         sizes = {"q_bias": self.q_heads * self.dim, "k_bias": self.kv_heads * self.dim, "v_bias": self.kv_heads * self.vdim}
-        specs += [TensorSpec(n[k], (sizes[k],), kind="vector", init="zeros") for k in self.biases]
+        specs += [TensorSpec(n[k], (sizes[k],), kind="vector") for k in self.biases]
         if self.value_blend == "blend":
-            specs.append(TensorSpec(n["value_blend_weight"], (), kind="vector", init="zeros"))
+            specs.append(TensorSpec(n["value_blend_weight"], (), kind="vector"))
         if self.position is not None:
             specs += self.position.tensor_specs()
         return specs
@@ -146,12 +149,12 @@ class Attention(Part):
         chunk = self.chunk or None
         if self.room is not None:
             return PagedKVNeed(self.kv_heads, self.room, self.window, chunk=chunk)
-        return PagedKVNeed(self.kv_heads, self.dim, self.window, self.vdim if self.vdim != self.dim else None, chunk=chunk)
+        return PagedKVNeed(self.kv_heads, self.k_room, self.window, self.v_room if self.v_room != self.k_room else None, chunk=chunk)
 
     def _on_tensor_cores(self, dtype) -> bool:
         """Whether the general path runs on the tensor-core kernels in a run of `dtype`."""
-        return (self.general and dtype == torch.bfloat16 and self.dim % 16 == 0 and self.vdim % 16 == 0
-                and self.q_heads // self.kv_heads <= 16)
+        return (self.general and dtype == torch.bfloat16 and self.q_heads // self.kv_heads <= 16
+                and (self.rows32 or (self.dim % 16 == 0 and self.vdim % 16 == 0)))     # rows32: any size, padded to 16s
 
     def parts(self):
         return [self.position] if self.position is not None else []
@@ -216,12 +219,13 @@ class Attention(Part):
             self.position.bind(tensors, runtime)
         if self._on_tensor_cores(runtime.dtype):
             ops.attention_scratch(runtime.device)      # made now, never inside a graph capture
-            self.room = max(self.dim, self.vdim)
-            # the heads' outputs arrive padded: zero columns in the output matrix (a channel gate writes them dense)
-            if self.room != self.vdim and not ("gate" in n and self.gate_kind == "channel"):
-                wide = torch.zeros((self.hidden, self.q_heads, self.room), dtype=self.w_o.dtype, device=self.w_o.device)
-                wide[:, :, : self.vdim] = self.w_o.view(self.hidden, self.q_heads, self.vdim)
-                self.w_o = wide.view(self.hidden, self.q_heads * self.room).contiguous()
+            self.room = -(-max(self.dim, self.vdim) // 16) * 16
+        # the heads' outputs arrive padded: zero columns in the output matrix (a channel gate writes them dense)
+        out_room = self.room or self.v_room
+        if out_room != self.vdim and not ("gate" in n and self.gate_kind == "channel"):
+            wide = torch.zeros((self.hidden, self.q_heads, out_room), dtype=self.w_o.dtype, device=self.w_o.device)
+            wide[:, :, : self.vdim] = self.w_o.view(self.hidden, self.q_heads, self.vdim)
+            self.w_o = wide.view(self.hidden, self.q_heads * out_room).contiguous()
 
     def _kept_values(self, batch, tokens, device):
         """The step's buffer of kept values [T, kv_heads * v_head_dim], 32-bit: made by the layer that keeps,
@@ -235,7 +239,7 @@ class Attention(Part):
 
     def _forward_general(self, h, batch, cache):
         tokens, group = h.shape[0], batch.groups[cache.group]
-        room = self.room or self.dim
+        room = self.room or self.k_room
         q = torch.empty((tokens, self.q_heads * room), dtype=h.dtype, device=h.device)
         gates = None
         if self.rows32:
@@ -259,9 +263,9 @@ class Attention(Part):
             ops.attention_bf16(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, room, cache.page_tokens,
                                self.scale, self.window or 0, sinks=self.sink, gates=gates, exact_weights=True, chunk=self.chunk)
         else:
-            out = torch.empty((tokens, self.q_heads * self.vdim), dtype=h.dtype, device=h.device)
-            ops.attention_f32(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.dim, cache.page_tokens,
-                              self.scale, self.window or 0, self.vdim, self.sink, gates, chunk=self.chunk)
+            out = torch.empty((tokens, self.q_heads * self.v_room), dtype=h.dtype, device=h.device)
+            ops.attention_f32(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.k_room, cache.page_tokens,
+                              self.scale, self.window or 0, self.v_room, self.sink, gates, chunk=self.chunk)
         if self.rows32 and "gate" in self.names:
             at = self.q_heads * self.dim + self.kv_heads * (self.dim + self.vdim)
             gated = torch.empty((tokens, self.q_heads * self.vdim), dtype=h.dtype, device=h.device)

@@ -98,7 +98,7 @@ class LayerNorm(Part):
     def tensor_specs(self):
         specs = [TensorSpec(self.weight_name, (self.dim,), kind="vector", init="ones")]
         if self.bias_name:
-            specs.append(TensorSpec(self.bias_name, (self.dim,), kind="vector", init="zeros"))
+            specs.append(TensorSpec(self.bias_name, (self.dim,), kind="vector"))
         return specs
 
     def bind(self, tensors, runtime):
