@@ -170,7 +170,7 @@ def test_chunked_attention_sees_exactly_its_chunk(dtype, heads, kv, d, e, chunk)
             rows = rows.to(dtype).float()
             want = plain_identity_attention(rows, sizes, heads, kv, d, e, chunk, scale)
             for cuts in ([n], [query, n - query], [n - 9] + [1] * 9, [3, 2, n - 5]):
-                got = run_cuts(cache, step, rows, cuts)[:, : heads * e]
+                got = run_cuts(cache, step, rows, [c for c in cuts if c])[:, : heads * e]
                 close(got, want, dtype, f"query {query}, target {target}, cuts {cuts[:3]}")
     cache.check()
 
