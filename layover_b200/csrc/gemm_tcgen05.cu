@@ -468,7 +468,12 @@ template <int BN, bool SWAP, typename OutT, int EPI, bool PAIR = false>
 __global__ void __launch_bounds__(persistent_threads(EPI), Tile<BN, SWAP, PAIR>::BLOCKS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OutT* __restrict__ C, long ldc, int rows_a, int rows_b, const Schedule sch,
-                    float* __restrict__ partials, unsigned* __restrict__ counters, bool vector_ok, const HeadsEpilogue he) {
+                    float* __restrict__ partials, unsigned* __restrict__ counters, bool vector_ok, const HeadsEpilogue he,
+                    const int* __restrict__ tile_b_rows = nullptr) {
+  // GROUPED products (single blocks, tokens on the 128-row side): `tile_b_rows`, one entry per tile of 128 rows of A,
+  // written on the device by an earlier kernel. Entry >= 0: the tile's rows all belong to one group whose weights
+  // start at that row of B (B stacks every group's [rows_b, K] matrix); entry < 0: the tile holds no row and is
+  // skipped by every role alike. The roles count the tiles they really run (`live`) for buffers and phases.
   static_assert(!(PAIR && SWAP), "pairs of blocks serve the many-token orientation");
   static_assert(EPI != 2 || (PAIR && BN == 256 && sizeof(OutT) == 2), "the q/k/v epilogue takes a pair's 256-column tiles of bfloat16");
   using T = Tile<BN, SWAP, PAIR>;
@@ -538,9 +543,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // tiles is requested before waiting for the kernel that produces the activations.
       int it = 0;                       // K blocks issued so far, over all segments
       bool waited = false;
+      if (tile_b_rows) {                // which weights a tile needs is itself an earlier kernel's output
+        pdl_wait();
+        waited = true;
+      }
       for (int j = 0; j < n_segments && !flag[0]; ++j) {
         const Segment seg = segment_at(sch, block, blocks, j);
-        const int m0 = (seg.tile % sch.tiles_m) * BM, n0 = (seg.tile / sch.tiles_m) * BN;
+        const int group_row = tile_b_rows ? tile_b_rows[seg.tile % sch.tiles_m] : 0;
+        if (group_row < 0) continue;
+        const int m0 = (seg.tile % sch.tiles_m) * BM, n0 = (seg.tile / sch.tiles_m) * BN + group_row;
         for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb, ++it) {
           const int s = it % T::STAGES;
           const uint32_t phase = (it / T::STAGES) & 1;
@@ -586,11 +597,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0 && rank == 0) {
       // ---------------- MMA issuer
       constexpr uint32_t idesc = instr_desc(BN, TILE_ROWS);
-      int it = 0;
+      int it = 0, live = 0;
+      if (tile_b_rows) pdl_wait();
       for (int j = 0; j < n_segments && !flag[0]; ++j) {
         const Segment seg = segment_at(sch, block, blocks, j);
-        const int buf = j & 1;
-        if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1)) { atomicCAS(&g_gemm_error, 0, 2); flag[0] = 1; break; }
+        if (tile_b_rows && tile_b_rows[seg.tile % sch.tiles_m] < 0) continue;
+        const int buf = live & 1;
+        if (!mbar_wait(&acc_empty[buf], ((live >> 1) & 1) ^ 1)) { atomicCAS(&g_gemm_error, 0, 2); flag[0] = 1; break; }
+        ++live;
         fence_after_sync();
         const uint32_t acc = tmem_base + buf * T::ACC_COLS;
         for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb, ++it) {
@@ -617,11 +631,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;                    // row of the 128-row side
     pdl_wait();   // the stores below touch memory that earlier kernels may still be reading
+    int live = 0;
     for (int j = 0; j < n_segments; ++j) {
       const Segment seg = segment_at(sch, block, blocks, j);
+      if (tile_b_rows && tile_b_rows[seg.tile % sch.tiles_m] < 0) continue;
       const int m0 = (seg.tile % sch.tiles_m) * TILE_ROWS + rank * BM, n0 = (seg.tile / sch.tiles_m) * BN;
-      const int buf = j & 1;
-      if (!mbar_wait(&acc_full[buf], (j >> 1) & 1)) { atomicCAS(&g_gemm_error, 0, 3); flag[0] = 1; break; }
+      const int buf = live & 1;
+      if (!mbar_wait(&acc_full[buf], (live >> 1) & 1)) { atomicCAS(&g_gemm_error, 0, 3); flag[0] = 1; break; }
+      ++live;
       fence_after_sync();
       const uint32_t lane_base = tmem_base + buf * T::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
       const int valid_cols = min(BN, rows_b - n0);
@@ -915,7 +932,7 @@ struct Problem {
 
 template <int BN, bool SWAP, typename OutT, int EPI = 0>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc, const Problem& pb, bool vector_ok,
-           cudaStream_t stream) {
+           cudaStream_t stream, const int* tile_b_rows = nullptr) {
   using T = Tile<BN, SWAP>;
   auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI>;
   static int blocks_per_sm = 0;      // how many blocks of this kernel an SM really holds (the same on every B200)
@@ -969,7 +986,8 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc
   }
   float* partials = sch.last_splits > 1 ? pb.scratch : nullptr;
   const int code = lb_launch(kernel, dim3(blocks), dim3(PERSISTENT_THREADS), (size_t)T::SMEM, stream, map_a, map_b,
-                             (OutT*)C, ldc, pb.rows_a, pb.rows_b, sch, partials, pb.counters, vector_ok, HeadsEpilogue{});
+                             (OutT*)C, ldc, pb.rows_a, pb.rows_b, sch, partials, pb.counters, vector_ok, HeadsEpilogue{},
+                             tile_b_rows);
   return code ? code : lb_last_error();
 }
 
@@ -1045,7 +1063,7 @@ int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, lon
   float* partials = sch.last_splits > 1 ? pb.scratch : nullptr;
   const int code = lb_launch_cluster_dims(kernel, dim3(2 * pairs), dim3(persistent_threads(EPI)), (size_t)T::SMEM, stream,
                                           dim3(2, 1, 1), map_a, map_b, (OutT*)C, ldc, pb.rows_a, pb.rows_b, sch, partials,
-                                          pb.counters, vector_ok, he);
+                                          pb.counters, vector_ok, he, (const int*)nullptr);
   return code ? code : lb_last_error();
 }
 
@@ -1237,6 +1255,41 @@ LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dty
   LB_GEMM_CASE(256, false)
 #undef LB_GEMM_CASE
   return LB_ERR_SIZE;
+}
+
+// Grouped products: C[M, N] where the rows of A come in tiles of 128 that each belong to ONE group g and are
+// multiplied by that group's weights W_g [N, K]; W stacks all groups' matrices ([groups * N, K], row stride ldw).
+// `tile_b_rows` (device, one int per tile of 128 rows of A, written by an earlier kernel of the stream) holds
+// g * N for a tile of group g and a negative number for a tile without rows, which costs nothing. M is the
+// number of rows A and C have room for (a multiple of 128 that the host knows without asking the device).
+// Always the many-token orientation on single blocks; `epilogue` as in `lb_gemm_tcgen05`.
+LB_EXPORT int lb_gemm_tcgen05_grouped(const void* A, const void* W, void* C, int out_dtype, int M, int N, int K, int groups,
+                                      long lda, long ldw, long ldc, const int* tile_b_rows, float* scratch,
+                                      long scratch_floats, unsigned* counters, int n_counters, int sm_count, int epilogue,
+                                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M % BM || groups <= 0 || !tile_b_rows) return LB_ERR_SIZE;
+  if (epilogue != 0 && epilogue != 1) return LB_ERR_SIZE;
+  if (epilogue == 1 && (N % 128 != 0 || out_dtype != LB_BF16)) return LB_ERR_SIZE;
+  if (!lb_gemm_tcgen05_supports(A, W, K, lda, ldw)) return LB_ERR_ALIGN;
+  if (out_dtype != LB_BF16 && out_dtype != LB_F32) return LB_ERR_DTYPE;
+  if (sm_count < 1) sm_count = 1;
+  const int bn = N > 128 ? 256 : 128;
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_b, W, (long)groups * N, K, ldw, bn)) return LB_ERR_ALIGN;
+  const Problem pb{M, N, K, bn, false, sm_count, 0, scratch, scratch_floats, counters, n_counters};
+  const int elem = out_dtype == LB_BF16 ? 2 : 4;
+  const bool vector_ok = ((uintptr_t)C % 16 == 0) && ((ldc * elem) % 16 == 0);
+  if (epilogue == 1) {
+    if (bn == 128) return launch<128, false, bf16, 1>(map_a, map_b, C, ldc, pb, vector_ok, stream, tile_b_rows);
+    return launch<256, false, bf16, 1>(map_a, map_b, C, ldc, pb, vector_ok, stream, tile_b_rows);
+  }
+  if (out_dtype == LB_BF16) {
+    if (bn == 128) return launch<128, false, bf16>(map_a, map_b, C, ldc, pb, vector_ok, stream, tile_b_rows);
+    return launch<256, false, bf16>(map_a, map_b, C, ldc, pb, vector_ok, stream, tile_b_rows);
+  }
+  if (bn == 128) return launch<128, false, float>(map_a, map_b, C, ldc, pb, vector_ok, stream, tile_b_rows);
+  return launch<256, false, float>(map_a, map_b, C, ldc, pb, vector_ok, stream, tile_b_rows);
 }
 
 // The q/k/v projection of `M` tokens fused with the per-head norm, the rotation and the page

@@ -99,6 +99,50 @@ moe_group_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __r
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) order[atomicAdd(&cursor[ids[i]], 1)] = i;
 }
 
+// The same grouping for the tensor-core products, whose tiles of 128 rows must each belong to one expert: expert
+// e's pairs take the places padded[e] .. padded[e] + count_e of buffers with room for pairs + 127 * experts rows
+// rounded up to 128, every padded[e] a multiple of 128. place_of[pair] is the pair's row there; tile_up[i] /
+// tile_down[i] = expert * rows_up / expert * rows_down for tile i of 128 rows (where that expert's weights start
+// in the stacked matrices), -1 for a tile without pairs.
+__global__ void __launch_bounds__(1024)
+moe_group_tiles_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ place_of,
+                       int* __restrict__ tile_up, int* __restrict__ tile_down, int n_tiles, int rows_up, int rows_down) {
+  extern __shared__ int counts[];                   // [experts] counts, then [experts] cursors
+  pdl_launch_dependents();
+  pdl_wait();
+  int* cursor = counts + experts;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+  for (int i = threadIdx.x; i < n_tiles; i += blockDim.x) { tile_up[i] = -1; tile_down[i] = -1; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&counts[ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts; ++e) {
+      cursor[e] = run;
+      const int tiles = (counts[e] + 127) >> 7;
+      for (int i = 0; i < tiles; ++i) { tile_up[(run >> 7) + i] = e * rows_up; tile_down[(run >> 7) + i] = e * rows_down; }
+      run += tiles << 7;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) place_of[i] = atomicAdd(&cursor[ids[i]], 1);
+}
+
+// rows[place_of[pair]] = T(scale[pair] * h[pair / top]): every pair's copy of its token's row, scaled by the pair's
+// score (scale null: copied), in the layout of the grouped products.
+template <typename T>
+__global__ void moe_scatter_rows_kernel(const T* __restrict__ h, long h_stride, const int* __restrict__ place_of,
+                                        const float* __restrict__ scale, T* __restrict__ rows, int hidden, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pair = blockIdx.x;
+  const T* src = h + (size_t)(pair / top) * h_stride;
+  T* dst = rows + (size_t)place_of[pair] * hidden;
+  const float s = scale ? scale[pair] : 1.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) Elem<T>::store(dst + i, s * Elem<T>::load(src + i));
+}
+
 template <int ACT> __device__ __forceinline__ float expert_activation(float g) {
   if (ACT == 1) return fmaxf(g, 0.f);
   return g / (1.0f + expf(-g));      // silu
@@ -117,7 +161,7 @@ moe_expert_product_kernel(const T* __restrict__ a, long a_stride, const int* __r
                           const int* __restrict__ offsets, int experts, const T* __restrict__ w, long expert_stride,
                           int n_out, int k_dim, OutT* __restrict__ out, long out_stride,
                           const int* __restrict__ out_rows, const float* __restrict__ pair_scale,
-                          const int* __restrict__ order) {
+                          const int* __restrict__ order, int interleaved) {
   constexpr int BK = 32, THREADS = (BM / TM) * (BN / TN);
   __shared__ float a_s[BK][BM + 1];
   __shared__ float w_s[GATED ? 2 : 1][BK][BN + 1];
@@ -165,8 +209,13 @@ moe_expert_product_kernel(const T* __restrict__ a, long a_stride, const int* __r
     for (int i = threadIdx.x; i < BN * BK; i += THREADS) {
       const int r = i / BK, c = i - r * BK;
       const bool live = n0 + r < n_out && k0 + c < k_dim;
-      w_s[0][c][r] = live ? Elem<T>::load(wg + (size_t)(n0 + r) * k_dim + k0 + c) : 0.f;
-      if (GATED) w_s[1][c][r] = live ? Elem<T>::load(wg + (size_t)(n_out + n0 + r) * k_dim + k0 + c) : 0.f;
+      // gate row n and up row n: the two halves of the matrix, or (interleaved) blocks of 64 gate rows followed by
+      // the 64 up rows of the same features, the layout of the tensor-core product's fused activation
+      const int n = n0 + r;
+      const size_t gate_row = (GATED && interleaved) ? (size_t)(n >> 6) * 128 + (n & 63) : (size_t)n;
+      const size_t up_row = (GATED && interleaved) ? gate_row + 64 : (size_t)n_out + n;
+      w_s[0][c][r] = live ? Elem<T>::load(wg + gate_row * k_dim + k0 + c) : 0.f;
+      if (GATED) w_s[1][c][r] = live ? Elem<T>::load(wg + up_row * k_dim + k0 + c) : 0.f;
     }
     __syncthreads();
 #pragma unroll 8
@@ -209,7 +258,7 @@ moe_expert_product_kernel(const T* __restrict__ a, long a_stride, const int* __r
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ pair_scale,
                                    const T* __restrict__ shared_out, const float* __restrict__ shared_factor,
-                                   T* __restrict__ out, long total, int hidden, int top) {
+                                   T* __restrict__ out, long total, int hidden, int top, const int* __restrict__ rows) {
   pdl_launch_dependents();
   pdl_wait();
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -217,7 +266,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
     const int c = (int)(i - t * hidden);
     float v = 0.f;
     for (int k = 0; k < top; ++k) {
-      const float part = y[(t * top + k) * hidden + c];
+      const float part = y[(rows ? (long)rows[t * top + k] : t * top + k) * hidden + c];
       v += pair_scale ? pair_scale[t * top + k] * part : part;
     }
     if (shared_out) v += (shared_factor ? shared_factor[t] : 1.f) * Elem<T>::load(shared_out + i);
@@ -228,9 +277,10 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
 template <typename T, bool GATED, typename OutT>
 int launch_product(bool few, int act, const void* a, long a_stride, const int* a_rows, int a_div, const int* offsets,
                    int experts, const void* w, long expert_stride, int n_out, int k_dim, void* out, long out_stride,
-                   const int* out_rows, const float* pair_scale, const int* order, int n_pairs, cudaStream_t stream) {
+                   const int* out_rows, const float* pair_scale, const int* order, int n_pairs, cudaStream_t stream,
+                   int interleaved = 0) {
 #define LB_MOE_ARGS (const T*)a, a_stride, a_rows, a_div, offsets, experts, (const T*)w, expert_stride, n_out, k_dim, \
-                    (OutT*)out, out_stride, out_rows, pair_scale, order
+                    (OutT*)out, out_stride, out_rows, pair_scale, order, interleaved
   if (few) {      // a handful of rows per expert: tiles of 8 places, so that the weights stream at the memory's rate
     constexpr int BM = 8, BN = 128;
     dim3 grid((n_pairs + BM - 1) / BM + experts, (n_out + BN - 1) / BN);
@@ -277,20 +327,22 @@ LB_EXPORT int lb_moe_group(const int* ids, int n_pairs, int experts, int* offset
 }
 
 // act[place, :] = T(act_fn(s g) * (s u)) for every place of `order`: h [tokens, hidden] (row stride h_stride), gate_up
-// [experts, 2 * inter, hidden] (gate rows, then up rows), scores by pair (null: s = 1). activation 0 silu, 1 relu.
+// [experts, 2 * inter, hidden] (gate rows, then up rows; `interleaved`: blocks of 64 gate rows + the 64 up rows of the same
+// features), scores by pair (null: s = 1). activation 0 silu, 1 relu.
 LB_EXPORT int lb_moe_expert_up(int dtype, const void* h, long h_stride, const int* order, const int* offsets,
                                const float* scores, const void* gate_up, void* act, int n_pairs, int top, int experts,
-                               int hidden, int inter, int activation, cudaStream_t stream) {
+                               int hidden, int inter, int activation, int interleaved, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
   if (experts <= 0 || hidden <= 0 || inter <= 0 || top <= 0 || activation < 0 || activation > 1) return LB_ERR_SIZE;
+  if (interleaved && inter % 64) return LB_ERR_SIZE;
   const bool few = n_pairs <= 4 * experts;
   const long expert_stride = 2L * inter * hidden;
   if (dtype == LB_F32)
     return launch_product<float, true, float>(few, activation, h, h_stride, order, top, offsets, experts, gate_up, expert_stride,
-                                              inter, hidden, act, inter, nullptr, scores, order, n_pairs, stream);
+                                              inter, hidden, act, inter, nullptr, scores, order, n_pairs, stream, interleaved);
   if (dtype == LB_BF16)
     return launch_product<bf16, true, bf16>(few, activation, h, h_stride, order, top, offsets, experts, gate_up, expert_stride,
-                                            inter, hidden, act, inter, nullptr, scores, order, n_pairs, stream);
+                                            inter, hidden, act, inter, nullptr, scores, order, n_pairs, stream, interleaved);
   return LB_ERR_DTYPE;
 }
 
@@ -310,9 +362,11 @@ LB_EXPORT int lb_moe_expert_down(int dtype, const void* act, const int* order, c
   return LB_ERR_DTYPE;
 }
 
-// out[t] = T(sum_k c_k y[t * top + k] + f_t shared_out[t]); c_k = pair_scale[t * top + k] or 1; f_t = shared_factor[t] or 1.
+// out[t] = T(sum_k c_k y[row(t * top + k)] + f_t shared_out[t]); c_k = pair_scale[t * top + k] or 1; f_t = shared_factor[t]
+// or 1; row(pair) = rows[pair], or the pair itself when rows is null.
 LB_EXPORT int lb_moe_combine(int dtype, const float* y, const float* pair_scale, const void* shared_out,
-                             const float* shared_factor, void* out, int tokens, int hidden, int top, cudaStream_t stream) {
+                             const float* shared_factor, void* out, int tokens, int hidden, int top, const int* rows,
+                             cudaStream_t stream) {
   const long total = (long)tokens * hidden;
   if (total <= 0) return 0;
   if (top <= 0) return LB_ERR_SIZE;
@@ -320,10 +374,36 @@ LB_EXPORT int lb_moe_combine(int dtype, const float* y, const float* pair_scale,
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == LB_F32)
     lb_launch(moe_combine_kernel<float>, blocks, threads, 0, stream, y, pair_scale, (const float*)shared_out, shared_factor,
-              (float*)out, total, hidden, top);
+              (float*)out, total, hidden, top, rows);
   else if (dtype == LB_BF16)
     lb_launch(moe_combine_kernel<bf16>, blocks, threads, 0, stream, y, pair_scale, (const bf16*)shared_out, shared_factor,
-              (bf16*)out, total, hidden, top);
+              (bf16*)out, total, hidden, top, rows);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
+// The grouping for the tensor-core products (see moe_group_tiles_kernel): n_tiles = the tiles of 128 rows the buffers have.
+LB_EXPORT int lb_moe_group_tiles(const int* ids, int n_pairs, int experts, int* place_of, int* tile_up, int* tile_down,
+                                 int n_tiles, int rows_up, int rows_down, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (experts <= 0 || experts > 4096 || (long)n_tiles * 128 < (long)n_pairs + 127L * experts) return LB_ERR_SIZE;
+  lb_launch(moe_group_tiles_kernel, 1, 1024, (size_t)2 * experts * sizeof(int), stream, ids, n_pairs, experts, place_of,
+            tile_up, tile_down, n_tiles, rows_up, rows_down);
+  return lb_last_error();
+}
+
+LB_EXPORT int lb_moe_scatter_rows(int dtype, const void* h, long h_stride, const int* place_of, const float* scale,
+                                  void* rows, int n_pairs, int hidden, int top, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (hidden <= 0 || top <= 0) return LB_ERR_SIZE;
+  const int threads = hidden >= 2048 ? 256 : 128;
+  if (dtype == LB_F32)
+    lb_launch(moe_scatter_rows_kernel<float>, n_pairs, threads, 0, stream, (const float*)h, h_stride, place_of, scale,
+              (float*)rows, hidden, top);
+  else if (dtype == LB_BF16)
+    lb_launch(moe_scatter_rows_kernel<bf16>, n_pairs, threads, 0, stream, (const bf16*)h, h_stride, place_of, scale,
+              (bf16*)rows, hidden, top);
   else
     return LB_ERR_DTYPE;
   return lb_last_error();

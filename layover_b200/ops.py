@@ -433,18 +433,21 @@ def moe_group(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: tor
 
 
 def moe_expert_up(h: torch.Tensor, order: torch.Tensor, offsets: torch.Tensor, scores: torch.Tensor | None,
-                  gate_up: torch.Tensor, act: torch.Tensor, top: int, activation: str = "silu") -> torch.Tensor:
+                  gate_up: torch.Tensor, act: torch.Tensor, top: int, activation: str = "silu",
+                  interleaved: bool = False) -> torch.Tensor:
     """act[place] = act_fn(s * gate_e h[token]) * (s * up_e h[token]) for every place of `order` (pair = token * top + k, s =
-    scores[pair] or 1): gate_up [experts, 2 * inter, H] (gate rows, then up rows), act [pairs, inter] in the run's type."""
+    scores[pair] or 1): gate_up [experts, 2 * inter, H] (gate rows, then up rows; `interleaved`: every expert's rows in
+    `interleave_gate_up`'s layout), act [pairs, inter] in the run's type."""
     _need(h, None, "h"); _need(gate_up, h.dtype, "gate_up"); _need(act, h.dtype, "act")
     experts, two_inter, hidden = gate_up.shape
     pairs = order.numel()
     if hidden != h.shape[1] or two_inter % 2 or tuple(act.shape) != (pairs, two_inter // 2) or pairs != h.shape[0] * top \
             or activation not in EXPERT_ACTIVATIONS:
         raise ValueError("moe_expert_up: shapes do not agree")
-    fn = _fn("moe", "lb_moe_expert_up", [c_int, c_void_p, c_long] + [c_void_p] * 5 + [c_int] * 6 + [c_void_p])
+    fn = _fn("moe", "lb_moe_expert_up", [c_int, c_void_p, c_long] + [c_void_p] * 5 + [c_int] * 7 + [c_void_p])
     _check(fn(dtype_code(h.dtype), _ptr(h), h.stride(0), _ptr(order), _ptr(offsets), _ptr(scores), _ptr(gate_up), _ptr(act),
-              pairs, int(top), experts, hidden, two_inter // 2, EXPERT_ACTIVATIONS[activation], _stream()), "moe_expert_up")
+              pairs, int(top), experts, hidden, two_inter // 2, EXPERT_ACTIVATIONS[activation], int(bool(interleaved)),
+              _stream()), "moe_expert_up")
     return act
 
 
@@ -462,13 +465,17 @@ def moe_expert_down(act: torch.Tensor, order: torch.Tensor, offsets: torch.Tenso
 
 
 def moe_combine(y: torch.Tensor, out: torch.Tensor, top: int, pair_scale: torch.Tensor | None = None,
-                shared_out: torch.Tensor | None = None, shared_factor: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t] = sum_k c_k y[t * top + k] + f_t shared_out[t], c = pair_scale or 1, f = shared_factor or 1; y float32
-    [T * top, H], out and shared_out [T, H] in the run's type."""
+                shared_out: torch.Tensor | None = None, shared_factor: torch.Tensor | None = None,
+                rows: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = sum_k c_k y[row(t * top + k)] + f_t shared_out[t], c = pair_scale or 1, f = shared_factor or 1; y float32
+    [T * top, H] (row(pair) = pair), or with `rows` (int32 [T * top]) any [R, H] with row(pair) = rows[pair]; out and
+    shared_out [T, H] in the run's type."""
     _need(y, torch.float32, "y"); _need(out, None, "out")
     tokens, hidden = out.shape
-    if tuple(y.shape) != (tokens * top, hidden):
-        raise ValueError("moe_combine: y must be [tokens * top, H]")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    if y.dim() != 2 or y.shape[1] != hidden or (rows is None and y.shape[0] != tokens * top) or (rows is not None and rows.numel() != tokens * top):
+        raise ValueError("moe_combine: y must be [tokens * top, H], or rows one entry per pair")
     if shared_out is not None:
         _need(shared_out, out.dtype, "shared_out")
         if shared_out.shape != out.shape:
@@ -476,9 +483,76 @@ def moe_combine(y: torch.Tensor, out: torch.Tensor, top: int, pair_scale: torch.
     for name, t in (("pair_scale", pair_scale), ("shared_factor", shared_factor)):
         if t is not None:
             _need(t, torch.float32, name)
-    fn = _fn("moe", "lb_moe_combine", [c_int] + [c_void_p] * 5 + [c_int] * 3 + [c_void_p])
+    fn = _fn("moe", "lb_moe_combine", [c_int] + [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_void_p])
     _check(fn(dtype_code(out.dtype), _ptr(y), _ptr(pair_scale), _ptr(shared_out), _ptr(shared_factor), _ptr(out), tokens, hidden,
-              int(top), _stream()), "moe_combine")
+              int(top), _ptr(rows), _stream()), "moe_combine")
+    return out
+
+
+MOE_TILE_ROWS = 128     # the tensor-core products take the pairs in tiles of this many rows, each of one expert
+
+
+def moe_padded_rows(pairs: int, experts: int) -> int:
+    """Rows of the buffers of the grouped tensor-core products: room for every expert's pairs rounded up to whole tiles."""
+    return -(-(pairs + (MOE_TILE_ROWS - 1) * experts) // MOE_TILE_ROWS) * MOE_TILE_ROWS
+
+
+def moe_group_tiles(ids: torch.Tensor, experts: int, place_of: torch.Tensor, tile_up: torch.Tensor, tile_down: torch.Tensor,
+                    rows_up: int, rows_down: int) -> None:
+    """The grouping for the tensor-core products: place_of[pair] = the pair's row in buffers of `moe_padded_rows` rows where
+    every tile of 128 rows belongs to one expert; tile_up[i] / tile_down[i] = expert * rows_up / expert * rows_down for tile
+    i (the row where that expert's weights begin in the stacked matrices), -1 for a tile without pairs."""
+    for name, t in (("ids", ids), ("place_of", place_of), ("tile_up", tile_up), ("tile_down", tile_down)):
+        _need(t, torch.int32, name)
+    if place_of.numel() != ids.numel() or tile_up.numel() != tile_down.numel() \
+            or tile_up.numel() * MOE_TILE_ROWS < moe_padded_rows(ids.numel(), experts):
+        raise ValueError("moe_group_tiles: place_of one entry per pair, the tile lists one per tile of the padded buffers")
+    fn = _fn("moe", "lb_moe_group_tiles", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(ids), ids.numel(), int(experts), _ptr(place_of), _ptr(tile_up), _ptr(tile_down), tile_up.numel(), int(rows_up),
+              int(rows_down), _stream()), "moe_group_tiles")
+
+
+def moe_scatter_rows(h: torch.Tensor, place_of: torch.Tensor, scale: torch.Tensor | None, rows: torch.Tensor, top: int) -> torch.Tensor:
+    """rows[place_of[pair]] = scale[pair] * h[pair // top] (scale None: a copy): h [T, H], rows [R, H] of h's type."""
+    _need(h, None, "h"); _need(rows, h.dtype, "rows"); _need(place_of, torch.int32, "place_of")
+    pairs = place_of.numel()
+    if pairs != h.shape[0] * top or rows.shape[1] != h.shape[1]:
+        raise ValueError("moe_scatter_rows: shapes do not agree")
+    if scale is not None:
+        _need(scale, torch.float32, "scale")
+    fn = _fn("moe", "lb_moe_scatter_rows", [c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(h.dtype), _ptr(h), h.stride(0), _ptr(place_of), _ptr(scale), _ptr(rows), pairs, h.shape[1], int(top),
+              _stream()), "moe_scatter_rows")
+    return rows
+
+
+def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_rows: torch.Tensor, groups: int,
+                         epilogue: str | None = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w_g[N, K]^T tile by tile: every tile of 128 rows of `a` is multiplied by the weights of ONE
+    group, the [N, K] matrix that begins at row tile_rows[tile] of w [groups * N, K]; tiles whose entry is negative are
+    skipped. tile_rows is int32 on the device, written by an earlier kernel. M is a multiple of 128. epilogue "swiglu" as in
+    `gemm_tcgen05` (each group's rows interleaved by `interleave_gate_up`)."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != 2:
+        raise ValueError("gemm_tcgen05_grouped: operands must be 2-D bfloat16")
+    m, k = a.shape
+    if w.shape[0] % groups or w.shape[1] != k or m % MOE_TILE_ROWS:
+        raise ValueError("gemm_tcgen05_grouped: shapes do not agree")
+    n = w.shape[0] // groups
+    if epilogue not in (None, "swiglu"):
+        raise ValueError(f"gemm_tcgen05_grouped: unknown epilogue {epilogue!r}")
+    out_cols = n // 2 if epilogue == "swiglu" else n
+    if epilogue == "swiglu" and (n % (2 * SWIGLU_BLOCK) or out.dtype != torch.bfloat16):
+        raise ValueError("gemm_tcgen05_grouped: the swiglu epilogue needs interleaved weights and a bfloat16 output")
+    _need(tile_rows, torch.int32, "tile_rows")
+    if tuple(out.shape) != (m, out_cols) or out.stride(1) != 1 or tile_rows.numel() < m // MOE_TILE_ROWS:
+        raise ValueError("gemm_tcgen05_grouped: out [M, N] and one tile entry per 128 rows")
+    partials, counters, sms = gemm_scratch(a.device)
+    fn = _fn("gemm_tcgen05", "lb_gemm_tcgen05_grouped",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_long, c_long, c_long, c_void_p, c_void_p, c_long,
+              c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), m, n, k, int(groups), a.stride(0), w.stride(0), out.stride(0),
+              _ptr(tile_rows), _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), sms,
+              1 if epilogue == "swiglu" else 0, _stream()), "gemm_tcgen05_grouped")
     return out
 
 

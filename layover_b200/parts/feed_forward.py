@@ -122,6 +122,13 @@ class RoutedExperts(Part):
     token's experts with the shared expert in the same kernel. Nothing comes back to the host in between,
     so a step with routed layers is captured in a CUDA graph like any other.
 
+    Two forms of the products. Few pairs (decode steps), and every float32 run: FFMA kernels that gather the
+    rows by index, take the score into the 32-bit sums and stream each chosen expert's weights once. Many
+    pairs in a bfloat16 run: the pairs' rows, scaled by their scores, are laid out expert by expert in tiles
+    of 128 rows (each expert's group padded to whole tiles), and both products run on the tensor cores as
+    ONE grouped launch each, a tile's weights chosen by a list that the grouping kernel leaves on the device;
+    tiles without pairs are skipped.
+
     params: hidden, experts, top, inter, activation ("silu"), router (tensor name), expert_gate / expert_up /
     expert_down (tensor names with `{}` for the expert's index), shared (a feed-forward PartSpec or None),
     shared_gate (tensor name of a [1, hidden] matrix, or None: the shared expert is added as it is)."""
@@ -163,14 +170,20 @@ class RoutedExperts(Part):
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
         self.router = tensors[self.router_name]
-        self.gate_up = torch.stack([torch.cat((tensors.pop(n["gate"]), tensors.pop(n["up"])), dim=0) for n in self.expert_names]).contiguous()
+        # one copy of the experts' weights serves both forms: where the tensor-core product can fuse the activation
+        # (bfloat16, silu, widths in blocks of 64) every expert's gate and up rows are interleaved for it
+        self.interleaved = (runtime.dtype == torch.bfloat16 and self.activation == "silu" and self.inter % ops.SWIGLU_BLOCK == 0)
+        stack = ops.interleave_gate_up if self.interleaved else (lambda gate, up: torch.cat((gate, up), dim=0))
+        self.gate_up = torch.stack([stack(tensors.pop(n["gate"]), tensors.pop(n["up"])) for n in self.expert_names]).contiguous()
         self.down = torch.stack([tensors.pop(n["down"]) for n in self.expert_names]).contiguous()
+        self.grouped = (runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0
+                        and ops.gemm_tcgen05_supports(self.gate_up.view(-1, self.hidden), self.down.view(-1, self.inter)))
         if self.shared is not None:
             self.shared.bind(tensors, runtime)
         self.shared_gate = tensors[self.shared_gate_name].reshape(-1).contiguous() if self.shared_gate_name else None
 
     def kernel_libraries(self, dtype):
-        return ("elementwise", "moe")
+        return ("elementwise", "moe") + (("gemm_tcgen05",) if dtype == torch.bfloat16 else ())
 
     def route(self, h: torch.Tensor):
         """(expert ids [T, top] int32, their scores [T, top] float32, the shared expert's factor [T] or None)."""
@@ -181,14 +194,42 @@ class RoutedExperts(Part):
         ops.moe_route(h, self.router, self.top, ids, scores, self.shared_gate, factor)
         return ids, scores, factor
 
+    GROUPED_FROM = 512      # pairs from which the grouped tensor-core products run (below: the FFMA kernels)
+
+    def _forward_grouped(self, h, ids, scores, factor):
+        tokens, pairs = h.shape[0], h.shape[0] * self.top
+        rows = ops.moe_padded_rows(pairs, self.experts)
+        tiles = rows // ops.MOE_TILE_ROWS
+        place_of = torch.empty((pairs,), dtype=torch.int32, device=h.device)
+        tile_up = torch.empty((tiles,), dtype=torch.int32, device=h.device)
+        tile_down = torch.empty((tiles,), dtype=torch.int32, device=h.device)
+        ops.moe_group_tiles(ids, self.experts, place_of, tile_up, tile_down, 2 * self.inter, self.hidden)
+        scaled = torch.empty((rows, self.hidden), dtype=h.dtype, device=h.device)
+        ops.moe_scatter_rows(h, place_of, scores, scaled, self.top)
+        act = torch.empty((rows, self.inter), dtype=h.dtype, device=h.device)
+        weights = self.gate_up.view(self.experts * 2 * self.inter, self.hidden)
+        if self.interleaved:
+            ops.gemm_tcgen05_grouped(scaled, weights, act, tile_up, self.experts, epilogue="swiglu")
+        else:
+            both = torch.empty((rows, 2 * self.inter), dtype=h.dtype, device=h.device)
+            ops.gemm_tcgen05_grouped(scaled, weights, both, tile_up, self.experts)
+            ops.gated_act(both, act, self.activation)
+        y = torch.empty((rows, self.hidden), dtype=torch.float32, device=h.device)
+        ops.gemm_tcgen05_grouped(act, self.down.view(self.experts * self.hidden, self.inter), y, tile_down, self.experts)
+        shared = self.shared.forward(h) if self.shared is not None else None
+        out = torch.empty((tokens, self.hidden), dtype=h.dtype, device=h.device)
+        return ops.moe_combine(y, out, self.top, None, shared, factor, rows=place_of)
+
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         tokens, pairs = h.shape[0], h.shape[0] * self.top
         ids, scores, factor = self.route(h)
+        if self.grouped and pairs >= self.GROUPED_FROM:
+            return self._forward_grouped(h, ids, scores, factor)
         offsets = torch.empty((self.experts + 1,), dtype=torch.int32, device=h.device)
         order = torch.empty((pairs,), dtype=torch.int32, device=h.device)
         ops.moe_group(ids, self.experts, offsets, order)
         act = torch.empty((pairs, self.inter), dtype=h.dtype, device=h.device)
-        ops.moe_expert_up(h, order, offsets, scores, self.gate_up, act, self.top, self.activation)
+        ops.moe_expert_up(h, order, offsets, scores, self.gate_up, act, self.top, self.activation, self.interleaved)
         y = torch.empty((pairs, self.hidden), dtype=torch.float32, device=h.device)
         ops.moe_expert_down(act, order, offsets, self.down, y)
         shared = self.shared.forward(h) if self.shared is not None else None

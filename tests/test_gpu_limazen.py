@@ -247,7 +247,11 @@ def routed_spec(hidden, experts, top, inter, shared):
 
 @pytest.mark.parametrize("dtype", list(DTYPES.values()))
 @pytest.mark.parametrize("hidden,experts,top,inter,shared,tokens", [(64, 8, 1, 24, 40, 50), (40, 5, 2, 12, 0, 3), (96, 3, 3, 70, 64, 200),
-                                                                    (128, 40, 4, 64, 128, 700), (32, 2, 1, 8, 16, 1)])
+                                                                    (128, 40, 4, 64, 128, 700), (32, 2, 1, 8, 16, 1),
+                                                                    # many pairs: in bfloat16 the grouped tensor-core products,
+                                                                    # with and without the activation in the first one
+                                                                    (96, 6, 2, 72, 0, 400), (256, 8, 2, 320, 64, 1500),
+                                                                    (64, 16, 1, 128, 0, 513)])
 def test_routed_experts_scale_their_input_by_the_score(dtype, hidden, experts, top, inter, shared, tokens):
     gen = torch.Generator().manual_seed(hidden + experts)
     t = {k: v.to(dtype).float() for k, v in expert_tensors(gen, experts, hidden, inter, shared).items()}
