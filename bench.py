@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights of a named Qwen3 shape.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--config 4b|4b-fp32|8b-mixed|32b-long|topidra]
+                    [--config 4b|4b-fp32|8b-mixed|32b-long|topidra|limazen]
 
 A step is one decode step. Every run prints ONE JSON line on standard output.
 
@@ -38,6 +38,11 @@ every sub-layer) beside Qwen3 at equal layer sizes, four layers each at three wi
 2,048 tokens and decode at batch 8 for both, then Topidra's own kernels alone with the like kernel
 of the Qwen3 path beside each, as microseconds and fractions of the measured peaks.
 
+--config limazen: the Limazen design (parallel blocks of chunked attention and a dense or routed
+feed-forward) beside Qwen3 at equal width, heads and active feed-forward width, four layers each at three
+sizes: prefill of 2,048 tokens and decode at batch 8 for both, then Limazen's own kernels alone with
+the like kernel of the Qwen3 path beside each.
+
 Peaks come from MEASURED_PEAKS.json beside this file when it exists (else 6.65 TB/s and
 1.59 PFLOP/s, an earlier measurement of the same kind of GPU). Inputs are synthetic token ids;
 weights are seeded random values of the named shape. Weights (8 GB and more) are larger than the
@@ -66,7 +71,7 @@ PROMPT, CONTEXT, PREFILL_TOKENS, PAGE = 2048, 4096, 2048, 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 FP32_TFLOPS = 75.0       # nominal FFMA rate of the part; only the 32-bit path's prefill fraction uses it
 CONFIGS = {"4b": ("qwen3-4b", "bf16"), "4b-fp32": ("qwen3-4b", "fp32"), "8b-mixed": ("qwen3-8b", "bf16"),
-           "32b-long": ("qwen3-32b", "bf16"), "topidra": ("topidra", "bf16")}
+           "32b-long": ("qwen3-32b", "bf16"), "topidra": ("topidra", "bf16"), "limazen": ("limazen", "bf16")}
 METRIC = "decode tokens/s (Qwen3-4B shape, batch 8, context 2048->4096)"
 
 
@@ -813,7 +818,10 @@ def step_bytes(model, batch: int, ctx: float) -> float:
     per_request = 0.0
     for _, need, reads in model.cache_needs():
         if isinstance(need, PagedKVNeed):
-            per_request += need.elements_per_token() * element * (min(ctx, need.window) if need.window else ctx)
+            seen = min(ctx, need.window) if need.window else ctx
+            if getattr(need, "chunk", None):        # a token sees the part of its chunk that lies behind it: half a chunk
+                seen = min(ctx, (need.chunk + 1) / 2)
+            per_request += need.elements_per_token() * element * seen
         elif isinstance(need, StateNeed):
             per_request += 2 * math.prod(need.shape) * 4
     return model.weight_bytes() + batch * per_request
@@ -845,6 +853,216 @@ def run_topidra(args, pk, pk_source) -> dict:
             "window": TOPIDRA_WINDOW, "sizes": sizes, "kernels": topidra_kernels(pk)}
 
 
+# --------------------------------------------------------------------------------------- Limazen beside Qwen3
+LIMAZEN_SIZES = {   # name: (width, query heads, KV heads, head size, experts, chosen, expert width, shared width); 0 experts: dense
+    "dense-2048": (2048, 16, 8, 128, 0, 0, 0, 8192),
+    "moe-2048": (2048, 16, 4, 128, 32, 4, 1024, 2048),
+    "moe-4096": (4096, 32, 8, 128, 64, 6, 1536, 3072)}
+LIMAZEN_LAYERS, LIMAZEN_VOCAB, LIMAZEN_CHUNK = 4, 32768, 1024
+
+
+def limazen_pair(size: str):
+    """(Limazen configuration, Qwen3 configuration) of equal width, heads and depth; the Qwen3 feed-forward is as
+    wide as what a Limazen token uses (its chosen experts and the shared one)."""
+    import layover_b200 as lb
+    from layover_b200.config.limazen import limazen_layer
+
+    width, heads, kv, dim, experts, top, expert_ff, shared = LIMAZEN_SIZES[size]
+    layer = limazen_layer(heads, kv, dim, dim, LIMAZEN_CHUNK, rot_dims=dim // 2, base=50000.0, factor=4.0,
+                          ff=None if experts else shared, experts=experts or None, top=top, expert_ff=expert_ff,
+                          shared_ff=shared if experts else None)
+    limazen = lb.LimazenConfig(vocab=LIMAZEN_VOCAB, width=width, layers=(layer,) * LIMAZEN_LAYERS, logit_softcap=30.0)
+    qwen = lb.Qwen3Config(vocab_size=LIMAZEN_VOCAB, hidden_size=width, intermediate_size=top * expert_ff + shared,
+                          num_hidden_layers=LIMAZEN_LAYERS, num_attention_heads=heads, num_key_value_heads=kv, head_dim=dim,
+                          max_position_embeddings=40960, tie_word_embeddings=False)
+    return limazen, qwen
+
+
+def limazen_kernels(pk: dict) -> dict:
+    """Limazen's own kernels alone at the moe-2048 layer size, each with the like kernel of the Qwen3 path:
+    microseconds (kernels back to back in a replayed graph, operands rotating through more memory than the L2
+    holds) and the fraction of the measured peak that bounds it."""
+    import torch
+    from layover_b200 import ops
+
+    width, heads, kv, dim, experts, top, expert_ff, shared = LIMAZEN_SIZES["moe-2048"]
+    dev, bf = "cuda", torch.bfloat16
+    hbm, tensor = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    out = {}
+
+    def point(name, fn, calls, nbytes=None, flops=None):
+        us = graph_time(fn, calls) * 1000.0
+        row = {"us": round(us, 2)}
+        if nbytes:
+            row["of_hbm"] = round(nbytes / (us * 1e-6) / hbm, 3)
+        if flops:
+            row["of_flops"] = round(flops / (us * 1e-6) / tensor, 3)
+        out[name] = row
+
+    ROT = 6
+    page = PAGE
+    nq, nk = heads * dim, kv * dim
+    for tokens in (2048, 8):
+        x = [torch.randn(tokens, width, device=dev) for _ in range(ROT)]
+        xb = [t.to(bf) for t in x]
+        da = [torch.randn(tokens, width, device=dev, dtype=bf) for _ in range(ROT)]
+        w = torch.ones(width, device=dev)
+        o = torch.empty(tokens, width, device=dev, dtype=bf)
+        point(f"residual_layernorm_{tokens}", lambda i: ops.residual_layernorm(x[i % ROT], da[i % ROT], da[(i + 1) % ROT], w, w, 1e-5, o),
+              ROT, nbytes=tokens * width * (4 + 4 + 2 + 2 + 2))
+        point(f"like:add_rmsnorm_{tokens}", lambda i: ops.add_rmsnorm(xb[i % ROT], da[i % ROT], w, 1e-6, o), ROT,
+              nbytes=tokens * width * (2 + 2 + 2 + 2))
+        # biases + partial rotation + value blend + page write, beside the per-head norm + rotation + page write
+        proj = [torch.randn(tokens, 2 * nq + 2 * nk, device=dev) for _ in range(ROT)]
+        projb = [torch.randn(tokens, nq + 2 * nk, device=dev, dtype=bf) for _ in range(ROT)]
+        pools = torch.zeros(2, tokens // page + 2, kv, page, dim, device=dev, dtype=bf)
+        slots = torch.arange(tokens, dtype=torch.int32, device=dev)
+        pos = torch.arange(tokens, dtype=torch.int32, device=dev)
+        part = torch.empty(tokens, 2, dim // 4, device=dev)
+        full = torch.empty(tokens, 2, dim // 2, device=dev)
+        ops.rope_table(pos, torch.rand(dim // 4, device=dev), part); ops.rope_table(pos, torch.rand(dim // 2, device=dev), full)
+        bq, bk = torch.randn(nq, device=dev), torch.randn(nk, device=dev)
+        kept, lam = torch.randn(tokens, nk, device=dev), torch.full((1,), 0.3, device=dev)
+        q = torch.empty(tokens, nq, device=dev, dtype=bf)
+        hd = torch.ones(dim, device=dev)
+        point(f"heads_bias_rope_kv_{tokens}", lambda i: ops.heads_bias_rope_kv(proj[i % ROT], q, pools[0], pools[1], bq, bk, bk, part,
+                                                                             slots, kept, 2, lam, heads, kv, dim, dim, page),
+              ROT, nbytes=tokens * ((nq + 2 * nk) * (4 + 2) + nk * 4))
+        point(f"like:qk_norm_rope_kv_{tokens}", lambda i: ops.qk_norm_rope_kv(projb[i % ROT], q, pools[0], pools[1], hd, hd, full, slots,
+                                                                             heads, kv, dim, page, 1e-6),
+              ROT, nbytes=tokens * (nq + 2 * nk) * (2 + 2))
+        attended = [torch.randn(tokens, nq, device=dev, dtype=bf) for _ in range(ROT)]
+        point(f"channel_gate_{tokens}", lambda i: ops.channel_gate(attended[i % ROT], proj[i % ROT][:, nq + 2 * nk:], q, heads, dim),
+              ROT, nbytes=tokens * nq * (2 + 4 + 2))
+        up = [torch.randn(tokens, shared, device=dev, dtype=bf) for _ in range(ROT)]
+        gu = [torch.randn(tokens, 2 * shared, device=dev, dtype=bf) for _ in range(ROT)]
+        act = torch.empty(tokens, shared, device=dev, dtype=bf)
+        point(f"relu2_{tokens}", lambda i: ops.activation(up[i % ROT], act, "relu2"), ROT, nbytes=tokens * shared * 4)
+        point(f"like:swiglu_{tokens}", lambda i: ops.swiglu(gu[i % ROT], act, block=ops.SWIGLU_BLOCK), ROT, nbytes=tokens * shared * 6)
+
+        # ---- routed experts: route, group, the two products, the sum; beside the dense products of equal work
+        h = [torch.randn(tokens, width, device=dev, dtype=bf) for _ in range(ROT)]
+        router = torch.randn(experts, width, device=dev)
+        sgw = torch.randn(width, device=dev)
+        ids = torch.empty(tokens, top, dtype=torch.int32, device=dev)
+        scores = torch.empty(tokens, top, device=dev)
+        factor = torch.empty(tokens, device=dev)
+        point(f"moe_route_{tokens}", lambda i: ops.moe_route(h[i % ROT], router, top, ids, scores, sgw, factor), ROT,
+              nbytes=tokens * width * 2 + (experts + 1) * width * 4)
+        pairs = tokens * top
+        gate_up = [torch.randn(experts * 2 * expert_ff, width, device=dev, dtype=bf) * 0.02 for _ in range(2)]
+        down = [torch.randn(experts * width, expert_ff, device=dev, dtype=bf) * 0.02 for _ in range(2)]
+        dense_gu = torch.randn(2 * top * expert_ff, width, device=dev, dtype=bf) * 0.02
+        dense_dn = torch.randn(width, top * expert_ff, device=dev, dtype=bf) * 0.02
+        y_dense = torch.empty(tokens, top * expert_ff, device=dev, dtype=bf)
+        o_dense = torch.empty(tokens, width, device=dev, dtype=bf)
+        ops.moe_route(h[0], router, top, ids, scores, sgw, factor)
+        up_flops, down_flops = 2.0 * pairs * 2 * expert_ff * width, 2.0 * pairs * width * expert_ff
+        if pairs >= 512:
+            rows = ops.moe_padded_rows(pairs, experts)
+            place = torch.empty(pairs, dtype=torch.int32, device=dev)
+            t_up = torch.empty(rows // 128, dtype=torch.int32, device=dev)
+            t_dn = torch.empty(rows // 128, dtype=torch.int32, device=dev)
+            point(f"moe_group_{tokens}", lambda i: ops.moe_group_tiles(ids, experts, place, t_up, t_dn, 2 * expert_ff, width), ROT)
+            scaled = torch.empty(rows, width, device=dev, dtype=bf)
+            point(f"moe_scatter_rows_{tokens}", lambda i: ops.moe_scatter_rows(h[i % ROT], place, scores, scaled, top), ROT,
+                  nbytes=pairs * width * 4)
+            acts = torch.empty(rows, expert_ff, device=dev, dtype=bf)
+            point(f"moe_experts_up_{tokens}", lambda i: ops.gemm_tcgen05_grouped(scaled, gate_up[i % 2], acts, t_up, experts, "swiglu"),
+                  2, flops=up_flops)
+            y = torch.empty(rows, width, device=dev)
+            point(f"moe_experts_down_{tokens}", lambda i: ops.gemm_tcgen05_grouped(acts, down[i % 2], y, t_dn, experts), 2, flops=down_flops)
+            point(f"like:gate_up_product_{tokens}", lambda i: ops.gemm_tcgen05(h[i % ROT], dense_gu, y_dense, epilogue="swiglu"), ROT,
+                  flops=2.0 * tokens * 2 * top * expert_ff * width)
+            point(f"like:down_product_{tokens}", lambda i: ops.gemm_tcgen05(y_dense, dense_dn, o_dense), ROT,
+                  flops=2.0 * tokens * width * top * expert_ff)
+            rows_of = place
+        else:
+            offsets = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+            order = torch.empty(pairs, dtype=torch.int32, device=dev)
+            point(f"moe_group_{tokens}", lambda i: ops.moe_group(ids, experts, offsets, order), ROT)
+            acts = torch.empty(pairs, expert_ff, device=dev, dtype=bf)
+            used = len(set(ids.flatten().tolist()))       # the experts this step reads
+            point(f"moe_experts_up_{tokens}", lambda i: ops.moe_expert_up(h[i % ROT], order, offsets, scores,
+                                                                         gate_up[i % 2].view(experts, 2 * expert_ff, width), acts, top,
+                                                                         "silu", True), 2, nbytes=used * 2 * expert_ff * width * 2)
+            y = torch.empty(pairs, width, device=dev)
+            point(f"moe_experts_down_{tokens}", lambda i: ops.moe_expert_down(acts, order, offsets, down[i % 2].view(experts, width, expert_ff), y),
+                  2, nbytes=used * expert_ff * width * 2)
+            wide_gu = [torch.randn(2 * used * expert_ff, width, device=dev, dtype=bf) * 0.02 for _ in range(2)]
+            wide_dn = [torch.randn(width, used * expert_ff, device=dev, dtype=bf) * 0.02 for _ in range(2)]
+            y_wide = torch.empty(tokens, used * expert_ff, device=dev, dtype=bf)
+            point(f"like:gate_up_product_{tokens}", lambda i: ops.gemm_tcgen05(h[i % ROT], wide_gu[i % 2], y_wide, epilogue="swiglu"), 2,
+                  nbytes=used * 2 * expert_ff * width * 2)
+            point(f"like:down_product_{tokens}", lambda i: ops.gemm_tcgen05(y_wide, wide_dn[i % 2], o_dense), 2,
+                  nbytes=used * expert_ff * width * 2)
+            rows_of = None
+        sh = torch.randn(tokens, width, device=dev, dtype=bf)
+        point(f"moe_combine_{tokens}", lambda i: ops.moe_combine(y, o, top, None, sh, factor, rows=rows_of), ROT,
+              nbytes=tokens * width * (top * 4 + 2 + 2))
+        del gate_up, down
+
+    # ---- chunked attention (weights with 16 bits of mantissa) beside the same kernels with a window and plain weights
+    for tokens, seqs, ctx in ((2048, 1, 2048), (8, 8, 3072), (64, 64, 3072)):
+        pages_per = -(-ctx // page)
+        pools = [torch.randn(2, seqs * pages_per + 1, kv, page, dim, device=dev, dtype=bf) for _ in range(ROT if seqs < 64 else 2)]
+        table = torch.arange(seqs * pages_per, dtype=torch.int32, device=dev).view(seqs, pages_per)
+        q = torch.randn(tokens, heads * dim, device=dev, dtype=bf)
+        o = torch.empty_like(q)
+        per = tokens // seqs
+        cu = torch.arange(0, tokens + 1, per, dtype=torch.int32, device=dev)
+        lens = torch.full((seqs,), ctx, dtype=torch.int32, device=dev)
+        R = len(pools)
+        if per > 1:
+            bq = ops.attention_mma_block_queries()
+            tq = torch.arange(0, per, bq, dtype=torch.int32, device=dev)
+            ts = torch.zeros_like(tq)
+            seen_pairs = sum(p % LIMAZEN_CHUNK + 1 for p in range(per))
+            window_pairs = sum(min(p + 1, LIMAZEN_CHUNK) for p in range(per))
+            for name, mask, extra, count in (("chunked_attention_prompt2048", -LIMAZEN_CHUNK, dict(exact_weights=True), 1.25 * seen_pairs),
+                                             ("like:attention_mma_prompt2048_window", LIMAZEN_CHUNK, {}, window_pairs)):
+                point(name, lambda i: ops.attention_prefill_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu, lens, ts, tq,
+                                                                 tq.numel(), heads, kv, dim, page, dim ** -0.5, mask, **extra),
+                      R, flops=4.0 * heads * dim * count)
+        else:
+            sms = ops.gemm_scratch(torch.device(dev))[2]
+            seen = (ctx - 1) % LIMAZEN_CHUNK + 1
+            splits, stages = ops.decode_plan(seqs, heads, kv, dim, LIMAZEN_CHUNK + 63, sms)
+            for name, mask, extra, keys in ((f"chunked_attention_decode_b{seqs}", -LIMAZEN_CHUNK, dict(exact_weights=True), seen),
+                                            (f"like:attention_decode_b{seqs}_window", LIMAZEN_CHUNK, {}, LIMAZEN_CHUNK)):
+                point(name, lambda i: ops.attention_decode_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu, lens, None, seqs,
+                                                                heads, kv, dim, page, dim ** -0.5, mask, splits, stages, **extra),
+                      R, nbytes=seqs * kv * keys * 2 * dim * 2)
+        del pools
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_limazen(args, pk, pk_source) -> dict:
+    import torch
+    import layover_b200 as lb
+
+    gen = torch.Generator().manual_seed(0)
+    sizes = {}
+    for size in LIMAZEN_SIZES:
+        row = {}
+        for name, cfg in zip(("limazen", "qwen3"), limazen_pair(size)):
+            model = lb.random_model(cfg, seed=0, device="cuda", dtype=args.dtype, std=0.02)
+            prefill = prefill_point(model, gen, repeats=5)
+            decode = decode_point(model, args.batch, min(args.steps, 64), args.warmup, gen)
+            row[name] = {"prefill_tok_s": round(prefill["tok_s"], 1), "prefill_ms": round(prefill["ms"], 3),
+                         "decode_tok_s": round(decode["tok_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                         "launches_per_step": round(decode["launches"] / min(args.steps, 64), 1),
+                         "weight_gb": round(model.weight_bytes() / 1e9, 3)}
+            del model
+            torch.cuda.empty_cache()
+        sizes[size] = row
+    return {"metric": "Limazen beside Qwen3 at equal width, heads and active feed-forward width: prefill of 2,048 tokens and "
+                      f"decode at batch {args.batch}, {LIMAZEN_LAYERS} layers, vocabulary {LIMAZEN_VOCAB}",
+            "dtype": args.dtype, "data": "synthetic token ids, seeded random weights", "peaks": pk_source,
+            "chunk": LIMAZEN_CHUNK, "sizes": sizes, "kernels": limazen_kernels(pk)}
+
+
 def lb_preset(name: str):
     import layover_b200 as lb
     return lb.preset(name)
@@ -863,6 +1081,8 @@ def run_ours(args) -> dict:
     pk, pk_source = peaks()
     if args.config == "topidra":
         return run_topidra(args, pk, pk_source)
+    if args.config == "limazen":
+        return run_limazen(args, pk, pk_source)
     if args.only == "kernels":
         return {"only": "kernels", **kernel_points(args.model, pk, with_library=True)}
     if args.only == "plans":
@@ -1008,7 +1228,7 @@ def main(argv=None) -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--config", default="4b", choices=sorted(CONFIGS),
                         help="4b: the headline; 4b-fp32: the 32-bit path; 8b-mixed: 32 mixed requests through the "
-                             "scheduler; 32b-long: 8 x 32,768-token contexts; topidra: the Topidra design beside "
+                             "scheduler; 32b-long: 8 x 32,768-token contexts; topidra / limazen: that design beside "
                              "Qwen3 at equal layer sizes, and its kernels alone")
     parser.add_argument("--model", default=None, help="a preset's name instead of the one --config names")
     parser.add_argument("--dtype", default=None, choices=["bf16", "fp32"])
