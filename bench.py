@@ -970,7 +970,7 @@ def limazen_kernels(pk: dict) -> dict:
             acts = torch.empty(rows, expert_ff, device=dev, dtype=bf)
             point(f"moe_experts_up_{tokens}", lambda i: ops.gemm_tcgen05_grouped(scaled, gate_up[i % 2], acts, t_up, experts, "swiglu"),
                   2, flops=up_flops)
-            y = torch.empty(rows, width, device=dev)
+            y = torch.empty(rows, width, device=dev, dtype=bf)
             point(f"moe_experts_down_{tokens}", lambda i: ops.gemm_tcgen05_grouped(acts, down[i % 2], y, t_dn, experts), 2, flops=down_flops)
             point(f"like:gate_up_product_{tokens}", lambda i: ops.gemm_tcgen05(h[i % ROT], dense_gu, y_dense, epilogue="swiglu"), ROT,
                   flops=2.0 * tokens * 2 * top * expert_ff * width)
@@ -999,7 +999,7 @@ def limazen_kernels(pk: dict) -> dict:
             rows_of = None
         sh = torch.randn(tokens, width, device=dev, dtype=bf)
         point(f"moe_combine_{tokens}", lambda i: ops.moe_combine(y, o, top, None, sh, factor, rows=rows_of), ROT,
-              nbytes=tokens * width * (top * 4 + 2 + 2))
+              nbytes=tokens * width * (top * y.element_size() + 2 + 2))
         del gate_up, down
 
     # ---- chunked attention (weights with 16 bits of mantissa) beside the same kernels with a window and plain weights

@@ -924,12 +924,25 @@ LB_EXPORT int lb_heads_bias_rope_kv(int dtype, const float* proj, long row_strid
 // out[t, h * vdim + c] = T(heads[t, h * room + c] * sigmoid(logits[t, h * vdim + c])): the gate of every
 // channel of the concatenated heads, from 32-bit logits that sit in a wider row (`logit_stride` floats
 // a token); the heads may come padded to `room` channels each, the output is dense.
-template <typename T>
+// VEC: four channels a thread (sizes, strides and addresses allow 16-byte accesses of the logits).
+template <typename T, bool VEC>
 __global__ void channel_gate_kernel(const T* __restrict__ heads, const float* __restrict__ logits, long logit_stride,
                                     T* __restrict__ out, long total, int q_heads, int vdim, int room) {
   pdl_launch_dependents();
   pdl_wait();
   const int width = q_heads * vdim;
+  if (VEC) {
+    for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < total; i += (long)gridDim.x * blockDim.x * 4) {
+      const long t = i / width;
+      const int j = (int)(i - t * width), h = j / vdim, c = j - h * vdim;
+      const float4 z = *reinterpret_cast<const float4*>(logits + t * logit_stride + j);
+      float4 v = Four<T>::load(heads + (t * q_heads + h) * room + c);
+      v.x *= 1.0f / (1.0f + expf(-z.x)); v.y *= 1.0f / (1.0f + expf(-z.y));
+      v.z *= 1.0f / (1.0f + expf(-z.z)); v.w *= 1.0f / (1.0f + expf(-z.w));
+      Four<T>::store(out + i, v);
+    }
+    return;
+  }
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     const long t = i / width;
     const int j = (int)(i - t * width), h = j / vdim, c = j - h * vdim;
@@ -944,15 +957,20 @@ LB_EXPORT int lb_channel_gate(int dtype, const void* heads, const float* logits,
   if (total <= 0) return 0;
   if (room < vdim) return LB_ERR_SIZE;
   const int threads = 256;
-  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-  if (dtype == LB_F32)
-    lb_launch(channel_gate_kernel<float>, blocks, threads, 0, stream, (const float*)heads, logits, logit_stride, (float*)out,
-              total, q_heads, vdim, room);
-  else if (dtype == LB_BF16)
-    lb_launch(channel_gate_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)heads, logits, logit_stride, (bf16*)out,
-              total, q_heads, vdim, room);
-  else
+  const bool vec = vdim % 4 == 0 && room % 4 == 0 && logit_stride % 4 == 0 && (uintptr_t)heads % 16 == 0 &&
+                   (uintptr_t)logits % 16 == 0 && (uintptr_t)out % 16 == 0;
+  const long items = vec ? total / 4 : total;
+  const int blocks = (int)((items + threads - 1) / threads < 148 * 16 ? (items + threads - 1) / threads : 148 * 16);
+#define LB_GATE_ARGS(T) (const T*)heads, logits, logit_stride, (T*)out, total, q_heads, vdim, room
+  if (dtype == LB_F32) {
+    if (vec) lb_launch(channel_gate_kernel<float, true>, blocks, threads, 0, stream, LB_GATE_ARGS(float));
+    else lb_launch(channel_gate_kernel<float, false>, blocks, threads, 0, stream, LB_GATE_ARGS(float));
+  } else if (dtype == LB_BF16) {
+    if (vec) lb_launch(channel_gate_kernel<bf16, true>, blocks, threads, 0, stream, LB_GATE_ARGS(bf16));
+    else lb_launch(channel_gate_kernel<bf16, false>, blocks, threads, 0, stream, LB_GATE_ARGS(bf16));
+  } else
     return LB_ERR_DTYPE;
+#undef LB_GATE_ARGS
   return lb_last_error();
 }
 

@@ -23,55 +23,109 @@
 
 namespace {
 
-constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_WARPS = 8;
 
-template <typename T>
+// Sixteen bytes of a row at once: 8 bfloat16 or 4 floats, as floats.
+template <typename T> struct Piece;
+template <> struct Piece<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  }
+};
+template <> struct Piece<bf16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 pair = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+      v[2 * i] = __low2float(pair);
+      v[2 * i + 1] = __high2float(pair);
+    }
+  }
+};
+
+// A block takes TT tokens; its warps share the experts (warp w takes experts w, w + 8, ...) and one more row for the
+// shared expert's factor. A logit is one warp's dot product: lane l holds the channels 4 (l + 32 i) .. + 3, multiplies
+// them in order, and the lanes' sums meet in a butterfly, the same order whatever TT is and whatever else the batch
+// holds. Then warp t picks token t's `top` experts. VEC: rows start on 16-byte boundaries and the width is a multiple
+// of 4 (router weights are read four at a time).
+template <typename T, int TT, bool VEC>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ shared_w,
                  int* __restrict__ ids, float* __restrict__ scores, float* __restrict__ shared_factor, int tokens,
                  int hidden, int experts, int top) {
-  extern __shared__ float logits[];                 // [ROUTE_WARPS][experts]
+  extern __shared__ float logits[];                 // [TT][experts]
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * ROUTE_WARPS + warp;
-  if (t >= tokens) return;
-  const T* row = h + (size_t)t * hidden;
-  float* z = logits + warp * experts;
-  for (int e = 0; e < experts; ++e) {
-    const float* w = router + (size_t)e * hidden;
-    float s = 0.f;
-    for (int i = lane; i < hidden; i += 32) s = fmaf(Elem<T>::load(row + i), w[i], s);
-    s = warp_sum(s);
-    if (lane == 0) z[e] = s;
-  }
-  if (shared_w) {
-    float s = 0.f;
-    for (int i = lane; i < hidden; i += 32) s = fmaf(Elem<T>::load(row + i), shared_w[i], s);
-    s = warp_sum(s);
-    if (lane == 0) shared_factor[t] = 1.0f / (1.0f + expf(-s));
-  }
-  __syncwarp();
-  for (int k = 0; k < top; ++k) {
-    float best = -INFINITY;
-    int at = 0x7fffffff;
-    for (int e = lane; e < experts; e += 32) {
-      const float v = z[e];
-      if (v > best || (v == best && e < at)) { best = v; at = e; }
+  const int t0 = blockIdx.x * TT, n_t = min(TT, tokens - t0);
+  for (int e = warp; e <= experts; e += ROUTE_WARPS) {
+    if (e == experts && !shared_w) break;
+    const float* w = e < experts ? router + (size_t)e * hidden : shared_w;
+    float acc[TT];
+#pragma unroll
+    for (int t = 0; t < TT; ++t) acc[t] = 0.f;
+    if (VEC) {
+      for (int i = lane * 4; i < hidden; i += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(w + i);
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+          if (t < n_t) {
+            const T* row = h + (size_t)(t0 + t) * hidden + i;
+            acc[t] = fmaf(Elem<T>::load(row), wv.x, acc[t]);
+            acc[t] = fmaf(Elem<T>::load(row + 1), wv.y, acc[t]);
+            acc[t] = fmaf(Elem<T>::load(row + 2), wv.z, acc[t]);
+            acc[t] = fmaf(Elem<T>::load(row + 3), wv.w, acc[t]);
+          }
+        }
+      }
+    } else {
+      for (int i0 = lane * 4; i0 < hidden; i0 += 128) {
+        for (int i = i0; i < min(i0 + 4, hidden); ++i) {
+          const float wv = w[i];
+#pragma unroll
+          for (int t = 0; t < TT; ++t)
+            if (t < n_t) acc[t] = fmaf(Elem<T>::load(h + (size_t)(t0 + t) * hidden + i), wv, acc[t]);
+        }
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    for (int t = 0; t < TT; ++t) {
+      const float s = warp_sum(acc[t]);
+      if (lane == 0 && t < n_t) {
+        if (e < experts) logits[t * experts + e] = s;
+        else shared_factor[t0 + t] = 1.0f / (1.0f + expf(-s));
+      }
     }
-    if (at >= experts) at = k;                      // only when every logit left is NaN or -inf
-    if (lane == 0) {
-      ids[(size_t)t * top + k] = at;
-      scores[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
-      z[at] = -INFINITY;                            // taken
+  }
+  __syncthreads();
+  for (int t = warp; t < n_t; t += ROUTE_WARPS) {
+    float* z = logits + t * experts;
+    for (int k = 0; k < top; ++k) {
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int e = lane; e < experts; e += 32) {
+        const float v = z[e];
+        if (v > best || (v == best && e < at)) { best = v; at = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+      }
+      if (at >= experts) at = k;                    // only when every logit left is NaN or -inf
+      if (lane == 0) {
+        ids[(size_t)(t0 + t) * top + k] = at;
+        scores[(size_t)(t0 + t) * top + k] = 1.0f / (1.0f + expf(-best));
+        z[at] = -INFINITY;                          // taken
+      }
+      __syncwarp();
     }
-    __syncwarp();
   }
 }
 
@@ -255,8 +309,94 @@ moe_expert_product_kernel(const T* __restrict__ a, long a_stride, const int* __r
   }
 }
 
-template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ pair_scale,
+// The experts' products for a handful of rows per expert (decode steps): a stream of the chosen experts' weights.
+// A block owns up to ROWS places of one expert's group and FEATURES output features per warp; a lane reads 16 bytes of
+// a weight row at a time (and the same channels of every row of the group, which the L1 holds), multiplies in the
+// order of k and the lanes' sums meet in a butterfly. GATED / interleaved / a_rows / out_rows / pair_scale as in the
+// tiled kernel above. Needs rows of `a` and `w` that start on 16-byte boundaries and k_dim a multiple of Piece<T>::N.
+constexpr int FEW_ROWS = 8, FEW_WARPS = 8;
+
+template <typename T, typename OutT, bool GATED, int ACT>
+__global__ void __launch_bounds__(FEW_WARPS * 32)
+moe_expert_rows_kernel(const T* __restrict__ a, long a_stride, const int* __restrict__ a_rows, int a_div,
+                       const int* __restrict__ offsets, int experts, const T* __restrict__ w, long expert_stride,
+                       int n_out, int k_dim, OutT* __restrict__ out, long out_stride,
+                       const int* __restrict__ out_rows, const float* __restrict__ pair_scale,
+                       const int* __restrict__ order, int interleaved, int features_per_warp) {
+  constexpr int N = Piece<T>::N;
+  __shared__ int tile_expert, tile_first, tile_rows;
+  __shared__ long row_of[FEW_ROWS];
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    int left = blockIdx.x, found = -1, first = 0, rows = 0;
+    for (int e = 0; e < experts && found < 0; ++e) {
+      const int begin = offsets[e], count = offsets[e + 1] - begin, tiles = (count + FEW_ROWS - 1) / FEW_ROWS;
+      if (left < tiles) {
+        found = e;
+        first = begin + left * FEW_ROWS;
+        rows = min(FEW_ROWS, count - left * FEW_ROWS);
+      }
+      left -= tiles;
+    }
+    tile_expert = found; tile_first = first; tile_rows = rows;
+    for (int r = 0; r < rows; ++r) row_of[r] = a_rows ? a_rows[first + r] / a_div : first + r;
+  }
+  __syncthreads();
+  const int expert = tile_expert, first = tile_first, rows = tile_rows;
+  if (expert < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* wg = w + (size_t)expert * expert_stride;
+  const int f0 = (blockIdx.y * FEW_WARPS + warp) * features_per_warp;
+  for (int n = f0; n < min(f0 + features_per_warp, n_out); ++n) {
+    const size_t gate_row = (GATED && interleaved) ? (size_t)(n >> 6) * 128 + (n & 63) : (size_t)n;
+    const size_t up_row = (GATED && interleaved) ? gate_row + 64 : (size_t)n_out + n;
+    const T* wr0 = wg + gate_row * k_dim;
+    const T* wr1 = wg + up_row * k_dim;
+    float acc[GATED ? 2 : 1][FEW_ROWS];
+#pragma unroll
+    for (int z = 0; z < (GATED ? 2 : 1); ++z)
+#pragma unroll
+      for (int r = 0; r < FEW_ROWS; ++r) acc[z][r] = 0.f;
+    for (int k = lane * N; k < k_dim; k += 32 * N) {
+      float w0[N], w1[N];
+      Piece<T>::load(wr0 + k, w0);
+      if (GATED) Piece<T>::load(wr1 + k, w1);
+#pragma unroll
+      for (int r = 0; r < FEW_ROWS; ++r) {
+        if (r < rows) {
+          float x[N];
+          Piece<T>::load(a + row_of[r] * a_stride + k, x);
+#pragma unroll
+          for (int i = 0; i < N; ++i) {
+            acc[0][r] = fmaf(x[i], w0[i], acc[0][r]);
+            if (GATED) acc[1][r] = fmaf(x[i], w1[i], acc[1][r]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < FEW_ROWS; ++r) {
+      if (r < rows) {            // uniform over the block
+        const float g = warp_sum(acc[0][r]);
+        const float u = GATED ? warp_sum(acc[GATED ? 1 : 0][r]) : 0.f;
+        if (lane == 0) {
+          const int place = first + r;
+          const long dst = out_rows ? out_rows[place] : place;
+          if (GATED) {
+            const float sc = pair_scale ? pair_scale[order[place]] : 1.f;
+            Elem<OutT>::store(out + dst * out_stride + n, expert_activation<ACT>(sc * g) * (sc * u));
+          } else {
+            Elem<OutT>::store(out + dst * out_stride + n, g);
+          }
+        }
+      }
+    }
+  }
+}
+
+template <typename T, typename YT>
+__global__ void moe_combine_kernel(const YT* __restrict__ y, const float* __restrict__ pair_scale,
                                    const T* __restrict__ shared_out, const float* __restrict__ shared_factor,
                                    T* __restrict__ out, long total, int hidden, int top, const int* __restrict__ rows) {
   pdl_launch_dependents();
@@ -266,7 +406,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
     const int c = (int)(i - t * hidden);
     float v = 0.f;
     for (int k = 0; k < top; ++k) {
-      const float part = y[(rows ? (long)rows[t * top + k] : t * top + k) * hidden + c];
+      const float part = Elem<YT>::load(y + (rows ? (long)rows[t * top + k] : t * top + k) * hidden + c);
       v += pair_scale ? pair_scale[t * top + k] * part : part;
     }
     if (shared_out) v += (shared_factor ? shared_factor[t] : 1.f) * Elem<T>::load(shared_out + i);
@@ -281,7 +421,18 @@ int launch_product(bool few, int act, const void* a, long a_stride, const int* a
                    int interleaved = 0) {
 #define LB_MOE_ARGS (const T*)a, a_stride, a_rows, a_div, offsets, experts, (const T*)w, expert_stride, n_out, k_dim, \
                     (OutT*)out, out_stride, out_rows, pair_scale, order, interleaved
-  if (few) {      // a handful of rows per expert: tiles of 8 places, so that the weights stream at the memory's rate
+  const bool aligned = (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0 && k_dim % Piece<T>::N == 0 &&
+                       (a_stride * sizeof(T)) % 16 == 0;
+  if (few && aligned) {     // a handful of rows per expert: a stream of the chosen experts' weight rows
+    // enough blocks to fill the GPU: the tiles are about the experts in use, the features are dealt over grid y
+    int tiles = (n_pairs + FEW_ROWS - 1) / FEW_ROWS + experts;
+    if (tiles > n_pairs) tiles = n_pairs;
+    int per_warp = 4;
+    while (per_warp > 1 && (long)tiles * ((n_out + FEW_WARPS * per_warp - 1) / (FEW_WARPS * per_warp)) < 4 * 148) per_warp >>= 1;
+    dim3 grid(tiles, (n_out + FEW_WARPS * per_warp - 1) / (FEW_WARPS * per_warp));
+    if (act == 1) lb_launch(moe_expert_rows_kernel<T, OutT, GATED, 1>, grid, FEW_WARPS * 32, 0, stream, LB_MOE_ARGS, per_warp);
+    else lb_launch(moe_expert_rows_kernel<T, OutT, GATED, 0>, grid, FEW_WARPS * 32, 0, stream, LB_MOE_ARGS, per_warp);
+  } else if (few) {      // the same through tiles of 8 places, for sizes and addresses that cannot be read 16 bytes at a time
     constexpr int BM = 8, BN = 128;
     dim3 grid((n_pairs + BM - 1) / BM + experts, (n_out + BN - 1) / BN);
     if (grid.x > (unsigned)n_pairs) grid.x = n_pairs;   // every tile holds a pair
@@ -300,22 +451,31 @@ int launch_product(bool few, int act, const void* a, long a_stride, const int* a
 
 }  // namespace
 
+template <typename T>
+static void launch_route(const void* h, const float* router, const float* shared_w, int* ids, float* scores,
+                         float* shared_factor, int tokens, int hidden, int experts, int top, cudaStream_t stream) {
+  const bool vec = hidden % 4 == 0 && (uintptr_t)router % 16 == 0 && (uintptr_t)shared_w % 16 == 0;
+  // few tokens: a block each, so that the step's latency is one token's; many: eight a block share every weight they read
+  if (tokens <= 64) {
+    const size_t smem = (size_t)experts * sizeof(float);
+    if (vec) lb_launch(moe_route_kernel<T, 1, true>, tokens, ROUTE_WARPS * 32, smem, stream, (const T*)h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top);
+    else lb_launch(moe_route_kernel<T, 1, false>, tokens, ROUTE_WARPS * 32, smem, stream, (const T*)h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top);
+  } else {
+    const size_t smem = (size_t)8 * experts * sizeof(float);
+    const int blocks = (tokens + 7) / 8;
+    if (vec) lb_launch(moe_route_kernel<T, 8, true>, blocks, ROUTE_WARPS * 32, smem, stream, (const T*)h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top);
+    else lb_launch(moe_route_kernel<T, 8, false>, blocks, ROUTE_WARPS * 32, smem, stream, (const T*)h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top);
+  }
+}
+
 LB_EXPORT int lb_moe_route(int dtype, const void* h, const float* router, const float* shared_w, int* ids, float* scores,
                            float* shared_factor, int tokens, int hidden, int experts, int top, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (hidden <= 0 || experts <= 0 || top <= 0 || top > experts || experts > 8192 || (shared_w && !shared_factor))
+  if (hidden <= 0 || experts <= 0 || top <= 0 || top > experts || experts > 1024 || (shared_w && !shared_factor))
     return LB_ERR_SIZE;
-  const size_t smem = (size_t)ROUTE_WARPS * experts * sizeof(float);
-  if (smem > 48 * 1024) return LB_ERR_SIZE;
-  const int blocks = (tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
-  if (dtype == LB_F32)
-    lb_launch(moe_route_kernel<float>, blocks, ROUTE_WARPS * 32, smem, stream, (const float*)h, router, shared_w, ids, scores,
-              shared_factor, tokens, hidden, experts, top);
-  else if (dtype == LB_BF16)
-    lb_launch(moe_route_kernel<bf16>, blocks, ROUTE_WARPS * 32, smem, stream, (const bf16*)h, router, shared_w, ids, scores,
-              shared_factor, tokens, hidden, experts, top);
-  else
-    return LB_ERR_DTYPE;
+  if (dtype == LB_F32) launch_route<float>(h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top, stream);
+  else if (dtype == LB_BF16) launch_route<bf16>(h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top, stream);
+  else return LB_ERR_DTYPE;
   return lb_last_error();
 }
 
@@ -363,8 +523,8 @@ LB_EXPORT int lb_moe_expert_down(int dtype, const void* act, const int* order, c
 }
 
 // out[t] = T(sum_k c_k y[row(t * top + k)] + f_t shared_out[t]); c_k = pair_scale[t * top + k] or 1; f_t = shared_factor[t]
-// or 1; row(pair) = rows[pair], or the pair itself when rows is null.
-LB_EXPORT int lb_moe_combine(int dtype, const float* y, const float* pair_scale, const void* shared_out,
+// or 1; row(pair) = rows[pair], or the pair itself when rows is null. y is 32-bit, or (y_dtype) in the run's type; the sum is 32-bit.
+LB_EXPORT int lb_moe_combine(int dtype, const void* y, int y_dtype, const float* pair_scale, const void* shared_out,
                              const float* shared_factor, void* out, int tokens, int hidden, int top, const int* rows,
                              cudaStream_t stream) {
   const long total = (long)tokens * hidden;
@@ -372,12 +532,15 @@ LB_EXPORT int lb_moe_combine(int dtype, const float* y, const float* pair_scale,
   if (top <= 0) return LB_ERR_SIZE;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-  if (dtype == LB_F32)
-    lb_launch(moe_combine_kernel<float>, blocks, threads, 0, stream, y, pair_scale, (const float*)shared_out, shared_factor,
-              (float*)out, total, hidden, top, rows);
-  else if (dtype == LB_BF16)
-    lb_launch(moe_combine_kernel<bf16>, blocks, threads, 0, stream, y, pair_scale, (const bf16*)shared_out, shared_factor,
-              (bf16*)out, total, hidden, top, rows);
+  if (dtype == LB_F32 && y_dtype == LB_F32)
+    lb_launch(moe_combine_kernel<float, float>, blocks, threads, 0, stream, (const float*)y, pair_scale, (const float*)shared_out,
+              shared_factor, (float*)out, total, hidden, top, rows);
+  else if (dtype == LB_BF16 && y_dtype == LB_F32)
+    lb_launch(moe_combine_kernel<bf16, float>, blocks, threads, 0, stream, (const float*)y, pair_scale, (const bf16*)shared_out,
+              shared_factor, (bf16*)out, total, hidden, top, rows);
+  else if (dtype == LB_BF16 && y_dtype == LB_BF16)
+    lb_launch(moe_combine_kernel<bf16, bf16>, blocks, threads, 0, stream, (const bf16*)y, pair_scale, (const bf16*)shared_out,
+              shared_factor, (bf16*)out, total, hidden, top, rows);
   else
     return LB_ERR_DTYPE;
   return lb_last_error();

@@ -467,10 +467,12 @@ def moe_expert_down(act: torch.Tensor, order: torch.Tensor, offsets: torch.Tenso
 def moe_combine(y: torch.Tensor, out: torch.Tensor, top: int, pair_scale: torch.Tensor | None = None,
                 shared_out: torch.Tensor | None = None, shared_factor: torch.Tensor | None = None,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t] = sum_k c_k y[row(t * top + k)] + f_t shared_out[t], c = pair_scale or 1, f = shared_factor or 1; y float32
-    [T * top, H] (row(pair) = pair), or with `rows` (int32 [T * top]) any [R, H] with row(pair) = rows[pair]; out and
-    shared_out [T, H] in the run's type."""
-    _need(y, torch.float32, "y"); _need(out, None, "out")
+    """out[t] = sum_k c_k y[row(t * top + k)] + f_t shared_out[t], c = pair_scale or 1, f = shared_factor or 1; y (float32,
+    or of out's type) [T * top, H] (row(pair) = pair), or with `rows` (int32 [T * top]) any [R, H] with row(pair) =
+    rows[pair]; out and shared_out [T, H] in the run's type. The sum is 32-bit."""
+    _need(y, None, "y"); _need(out, None, "out")
+    if y.dtype not in (torch.float32, out.dtype):
+        raise ValueError("moe_combine: y must be float32 or of out's type")
     tokens, hidden = out.shape
     if rows is not None:
         _need(rows, torch.int32, "rows")
@@ -483,9 +485,9 @@ def moe_combine(y: torch.Tensor, out: torch.Tensor, top: int, pair_scale: torch.
     for name, t in (("pair_scale", pair_scale), ("shared_factor", shared_factor)):
         if t is not None:
             _need(t, torch.float32, name)
-    fn = _fn("moe", "lb_moe_combine", [c_int] + [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_void_p])
-    _check(fn(dtype_code(out.dtype), _ptr(y), _ptr(pair_scale), _ptr(shared_out), _ptr(shared_factor), _ptr(out), tokens, hidden,
-              int(top), _ptr(rows), _stream()), "moe_combine")
+    fn = _fn("moe", "lb_moe_combine", [c_int, c_void_p, c_int] + [c_void_p] * 4 + [c_int] * 3 + [c_void_p, c_void_p])
+    _check(fn(dtype_code(out.dtype), _ptr(y), dtype_code(y.dtype), _ptr(pair_scale), _ptr(shared_out), _ptr(shared_factor), _ptr(out),
+              tokens, hidden, int(top), _ptr(rows), _stream()), "moe_combine")
     return out
 
 

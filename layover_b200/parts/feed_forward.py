@@ -214,7 +214,7 @@ class RoutedExperts(Part):
             both = torch.empty((rows, 2 * self.inter), dtype=h.dtype, device=h.device)
             ops.gemm_tcgen05_grouped(scaled, weights, both, tile_up, self.experts)
             ops.gated_act(both, act, self.activation)
-        y = torch.empty((rows, self.hidden), dtype=torch.float32, device=h.device)
+        y = torch.empty((rows, self.hidden), dtype=h.dtype, device=h.device)     # rounded like every product's output; summed in 32-bit
         ops.gemm_tcgen05_grouped(act, self.down.view(self.experts * self.hidden, self.inter), y, tile_down, self.experts)
         shared = self.shared.forward(h) if self.shared is not None else None
         out = torch.empty((tokens, self.hidden), dtype=h.dtype, device=h.device)

