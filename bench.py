@@ -958,11 +958,11 @@ def limazen_kernels(pk: dict) -> dict:
         o_dense = torch.empty(tokens, width, device=dev, dtype=bf)
         ops.moe_route(h[0], router, top, ids, scores, sgw, factor)
         up_flops, down_flops = 2.0 * pairs * 2 * expert_ff * width, 2.0 * pairs * width * expert_ff
-        if pairs >= 512:
+        if pairs > 4 * experts:
             rows = ops.moe_padded_rows(pairs, experts)
             place = torch.empty(pairs, dtype=torch.int32, device=dev)
-            t_up = torch.empty(rows // 128, dtype=torch.int32, device=dev)
-            t_dn = torch.empty(rows // 128, dtype=torch.int32, device=dev)
+            t_up = torch.empty(rows // 128 + 1, dtype=torch.int32, device=dev)
+            t_dn = torch.empty(rows // 128 + 1, dtype=torch.int32, device=dev)
             point(f"moe_group_{tokens}", lambda i: ops.moe_group_tiles(ids, experts, place, t_up, t_dn, 2 * expert_ff, width), ROT)
             scaled = torch.empty(rows, width, device=dev, dtype=bf)
             point(f"moe_scatter_rows_{tokens}", lambda i: ops.moe_scatter_rows(h[i % ROT], place, scores, scaled, top), ROT,

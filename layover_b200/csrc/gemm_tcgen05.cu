@@ -470,10 +470,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     OutT* __restrict__ C, long ldc, int rows_a, int rows_b, const Schedule sch,
                     float* __restrict__ partials, unsigned* __restrict__ counters, bool vector_ok, const HeadsEpilogue he,
                     const int* __restrict__ tile_b_rows = nullptr) {
-  // GROUPED products (single blocks, tokens on the 128-row side): `tile_b_rows`, one entry per tile of 128 rows of A,
-  // written on the device by an earlier kernel. Entry >= 0: the tile's rows all belong to one group whose weights
-  // start at that row of B (B stacks every group's [rows_b, K] matrix); entry < 0: the tile holds no row and is
-  // skipped by every role alike. The roles count the tiles they really run (`live`) for buffers and phases.
+  // GROUPED products (single blocks, tokens on the 128-row side): `tile_b_rows`, one entry per tile of 128 rows of A
+  // and one more, written on the device by an earlier kernel. Entry i: the rows of tile i all belong to one group
+  // whose weights start at that row of B (B stacks every group's [rows_b, K] matrix). The last entry is the number
+  // of row tiles in use, all at the front: the tiles are then numbered over those alone (so the blocks share the
+  // real work evenly) and tile numbers beyond them are skipped by every role alike. The roles count the tiles they
+  // really run (`live`) for buffers and phases.
   static_assert(!(PAIR && SWAP), "pairs of blocks serve the many-token orientation");
   static_assert(EPI != 2 || (PAIR && BN == 256 && sizeof(OutT) == 2), "the q/k/v epilogue takes a pair's 256-column tiles of bfloat16");
   using T = Tile<BN, SWAP, PAIR>;
@@ -543,15 +545,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // tiles is requested before waiting for the kernel that produces the activations.
       int it = 0;                       // K blocks issued so far, over all segments
       bool waited = false;
+      int tm = sch.tiles_m, live_tiles = sch.tiles;
       if (tile_b_rows) {                // which weights a tile needs is itself an earlier kernel's output
         pdl_wait();
         waited = true;
+        tm = max(1, min(tile_b_rows[sch.tiles_m], sch.tiles_m));
+        live_tiles = tm * (sch.tiles / sch.tiles_m);
       }
       for (int j = 0; j < n_segments && !flag[0]; ++j) {
         const Segment seg = segment_at(sch, block, blocks, j);
-        const int group_row = tile_b_rows ? tile_b_rows[seg.tile % sch.tiles_m] : 0;
-        if (group_row < 0) continue;
-        const int m0 = (seg.tile % sch.tiles_m) * BM, n0 = (seg.tile / sch.tiles_m) * BN + group_row;
+        if (seg.tile >= live_tiles) continue;
+        const int group_row = tile_b_rows ? max(0, tile_b_rows[seg.tile % tm]) : 0;
+        const int m0 = (seg.tile % tm) * BM, n0 = (seg.tile / tm) * BN + group_row;
         for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb, ++it) {
           const int s = it % T::STAGES;
           const uint32_t phase = (it / T::STAGES) & 1;
@@ -597,11 +602,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0 && rank == 0) {
       // ---------------- MMA issuer
       constexpr uint32_t idesc = instr_desc(BN, TILE_ROWS);
-      int it = 0, live = 0;
-      if (tile_b_rows) pdl_wait();
+      int it = 0, live = 0, live_tiles = sch.tiles;
+      if (tile_b_rows) {
+        pdl_wait();
+        live_tiles = max(1, min(tile_b_rows[sch.tiles_m], sch.tiles_m)) * (sch.tiles / sch.tiles_m);
+      }
       for (int j = 0; j < n_segments && !flag[0]; ++j) {
         const Segment seg = segment_at(sch, block, blocks, j);
-        if (tile_b_rows && tile_b_rows[seg.tile % sch.tiles_m] < 0) continue;
+        if (seg.tile >= live_tiles) continue;
         const int buf = live & 1;
         if (!mbar_wait(&acc_empty[buf], ((live >> 1) & 1) ^ 1)) { atomicCAS(&g_gemm_error, 0, 2); flag[0] = 1; break; }
         ++live;
@@ -632,10 +640,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int row = quarter * 32 + lane;                    // row of the 128-row side
     pdl_wait();   // the stores below touch memory that earlier kernels may still be reading
     int live = 0;
+    const int tm = tile_b_rows ? max(1, min(tile_b_rows[sch.tiles_m], sch.tiles_m)) : sch.tiles_m;
+    const int live_tiles = tm * (sch.tiles / sch.tiles_m);
     for (int j = 0; j < n_segments; ++j) {
       const Segment seg = segment_at(sch, block, blocks, j);
-      if (tile_b_rows && tile_b_rows[seg.tile % sch.tiles_m] < 0) continue;
-      const int m0 = (seg.tile % sch.tiles_m) * TILE_ROWS + rank * BM, n0 = (seg.tile / sch.tiles_m) * BN;
+      if (seg.tile >= live_tiles) continue;
+      const int m0 = (seg.tile % tm) * TILE_ROWS + rank * BM, n0 = (seg.tile / tm) * BN;
       const int buf = live & 1;
       if (!mbar_wait(&acc_full[buf], (live >> 1) & 1)) { atomicCAS(&g_gemm_error, 0, 3); flag[0] = 1; break; }
       ++live;
@@ -1259,8 +1269,9 @@ LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dty
 
 // Grouped products: C[M, N] where the rows of A come in tiles of 128 that each belong to ONE group g and are
 // multiplied by that group's weights W_g [N, K]; W stacks all groups' matrices ([groups * N, K], row stride ldw).
-// `tile_b_rows` (device, one int per tile of 128 rows of A, written by an earlier kernel of the stream) holds
-// g * N for a tile of group g and a negative number for a tile without rows, which costs nothing. M is the
+// `tile_b_rows` (device, one int per tile of 128 rows of A and one more, written by an earlier kernel of the
+// stream) holds g * N for a tile of group g; its last entry is the number of row tiles in use (all at the front,
+// the tiles behind them cost nothing). M is the
 // number of rows A and C have room for (a multiple of 128 that the host knows without asking the device).
 // Always the many-token orientation on single blocks; `epilogue` as in `lb_gemm_tcgen05`.
 LB_EXPORT int lb_gemm_tcgen05_grouped(const void* A, const void* W, void* C, int out_dtype, int M, int N, int K, int groups,

@@ -23,7 +23,6 @@
 
 namespace {
 
-constexpr int ROUTE_WARPS = 8;
 
 // Sixteen bytes of a row at once: 8 bfloat16 or 4 floats, as floats.
 template <typename T> struct Piece;
@@ -48,16 +47,17 @@ template <> struct Piece<bf16> {
   }
 };
 
-// A block takes TT tokens; its warps share the experts (warp w takes experts w, w + 8, ...) and one more row for the
-// shared expert's factor. A logit is one warp's dot product: lane l holds the channels 4 (l + 32 i) .. + 3, multiplies
-// them in order, and the lanes' sums meet in a butterfly, the same order whatever TT is and whatever else the batch
-// holds. Then warp t picks token t's `top` experts. VEC: rows start on 16-byte boundaries and the width is a multiple
-// of 4 (router weights are read four at a time).
-template <typename T, int TT, bool VEC>
-__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+// A block takes TT tokens; its warps share the experts (warp w takes experts w, w + WARPS, ...) and one more row for the
+// shared expert's factor. A logit is one warp's dot product: lane l holds the channels N (l + 32 i) .. + N - 1 (N = 16
+// bytes of h), multiplies them in order, and the lanes' sums meet in a butterfly, the same order whatever TT is and
+// whatever else the batch holds. Then warp t picks token t's `top` experts. VEC: rows start on 16-byte boundaries and
+// the width is a multiple of N.
+template <typename T, int TT, int WARPS, bool VEC>
+__global__ void __launch_bounds__(WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ shared_w,
                  int* __restrict__ ids, float* __restrict__ scores, float* __restrict__ shared_factor, int tokens,
                  int hidden, int experts, int top) {
+  constexpr int N = Piece<T>::N, ROUTE_WARPS = WARPS;
   extern __shared__ float logits[];                 // [TT][experts]
   pdl_launch_dependents();
   pdl_wait();
@@ -70,22 +70,26 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
 #pragma unroll
     for (int t = 0; t < TT; ++t) acc[t] = 0.f;
     if (VEC) {
-      for (int i = lane * 4; i < hidden; i += 128) {
-        const float4 wv = *reinterpret_cast<const float4*>(w + i);
+      for (int i = lane * N; i < hidden; i += 32 * N) {
+        float wv[N];
+#pragma unroll
+        for (int c = 0; c < N; c += 4) {
+          const float4 r = *reinterpret_cast<const float4*>(w + i + c);
+          wv[c] = r.x; wv[c + 1] = r.y; wv[c + 2] = r.z; wv[c + 3] = r.w;
+        }
 #pragma unroll
         for (int t = 0; t < TT; ++t) {
           if (t < n_t) {
-            const T* row = h + (size_t)(t0 + t) * hidden + i;
-            acc[t] = fmaf(Elem<T>::load(row), wv.x, acc[t]);
-            acc[t] = fmaf(Elem<T>::load(row + 1), wv.y, acc[t]);
-            acc[t] = fmaf(Elem<T>::load(row + 2), wv.z, acc[t]);
-            acc[t] = fmaf(Elem<T>::load(row + 3), wv.w, acc[t]);
+            float x[N];
+            Piece<T>::load(h + (size_t)(t0 + t) * hidden + i, x);
+#pragma unroll
+            for (int c = 0; c < N; ++c) acc[t] = fmaf(x[c], wv[c], acc[t]);
           }
         }
       }
     } else {
-      for (int i0 = lane * 4; i0 < hidden; i0 += 128) {
-        for (int i = i0; i < min(i0 + 4, hidden); ++i) {
+      for (int i0 = lane * N; i0 < hidden; i0 += 32 * N) {
+        for (int i = i0; i < min(i0 + N, hidden); ++i) {
           const float wv = w[i];
 #pragma unroll
           for (int t = 0; t < TT; ++t)
@@ -157,7 +161,7 @@ moe_group_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __r
 // e's pairs take the places padded[e] .. padded[e] + count_e of buffers with room for pairs + 127 * experts rows
 // rounded up to 128, every padded[e] a multiple of 128. place_of[pair] is the pair's row there; tile_up[i] /
 // tile_down[i] = expert * rows_up / expert * rows_down for tile i of 128 rows (where that expert's weights start
-// in the stacked matrices), -1 for a tile without pairs.
+// in the stacked matrices), -1 for a tile without pairs; one more entry behind the tiles' holds the number of tiles in use.
 __global__ void __launch_bounds__(1024)
 moe_group_tiles_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ place_of,
                        int* __restrict__ tile_up, int* __restrict__ tile_down, int n_tiles, int rows_up, int rows_down) {
@@ -178,6 +182,8 @@ moe_group_tiles_kernel(const int* __restrict__ ids, int n_pairs, int experts, in
       for (int i = 0; i < tiles; ++i) { tile_up[(run >> 7) + i] = e * rows_up; tile_down[(run >> 7) + i] = e * rows_down; }
       run += tiles << 7;
     }
+    tile_up[n_tiles] = run >> 7;      // the tiles in use, all at the front
+    tile_down[n_tiles] = run >> 7;
   }
   __syncthreads();
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) place_of[i] = atomicAdd(&cursor[ids[i]], 1);
@@ -314,7 +320,7 @@ moe_expert_product_kernel(const T* __restrict__ a, long a_stride, const int* __r
 // a weight row at a time (and the same channels of every row of the group, which the L1 holds), multiplies in the
 // order of k and the lanes' sums meet in a butterfly. GATED / interleaved / a_rows / out_rows / pair_scale as in the
 // tiled kernel above. Needs rows of `a` and `w` that start on 16-byte boundaries and k_dim a multiple of Piece<T>::N.
-constexpr int FEW_ROWS = 8, FEW_WARPS = 8;
+constexpr int FEW_ROWS = 4, FEW_WARPS = 8, FEW_FEATURES = 2;
 
 template <typename T, typename OutT, bool GATED, int ACT>
 __global__ void __launch_bounds__(FEW_WARPS * 32)
@@ -323,7 +329,7 @@ moe_expert_rows_kernel(const T* __restrict__ a, long a_stride, const int* __rest
                        int n_out, int k_dim, OutT* __restrict__ out, long out_stride,
                        const int* __restrict__ out_rows, const float* __restrict__ pair_scale,
                        const int* __restrict__ order, int interleaved, int features_per_warp) {
-  constexpr int N = Piece<T>::N;
+  constexpr int N = Piece<T>::N, Z = GATED ? 2 : 1, F = FEW_FEATURES;
   __shared__ int tile_expert, tile_first, tile_rows;
   __shared__ long row_of[FEW_ROWS];
   pdl_launch_dependents();
@@ -348,46 +354,59 @@ moe_expert_rows_kernel(const T* __restrict__ a, long a_stride, const int* __rest
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* wg = w + (size_t)expert * expert_stride;
   const int f0 = (blockIdx.y * FEW_WARPS + warp) * features_per_warp;
-  for (int n = f0; n < min(f0 + features_per_warp, n_out); ++n) {
-    const size_t gate_row = (GATED && interleaved) ? (size_t)(n >> 6) * 128 + (n & 63) : (size_t)n;
-    const size_t up_row = (GATED && interleaved) ? gate_row + 64 : (size_t)n_out + n;
-    const T* wr0 = wg + gate_row * k_dim;
-    const T* wr1 = wg + up_row * k_dim;
-    float acc[GATED ? 2 : 1][FEW_ROWS];
+  for (int n0 = f0; n0 < min(f0 + features_per_warp, n_out); n0 += F) {
+    // F features at once, so that a lane has 2 F (gated) rows of weights on their way at any time
+    const T* wr[Z][F];
 #pragma unroll
-    for (int z = 0; z < (GATED ? 2 : 1); ++z)
+    for (int f = 0; f < F; ++f) {
+      const int n = min(n0 + f, n_out - 1);           // a feature past the end repeats the last one and is not stored
+      const size_t gate_row = (GATED && interleaved) ? (size_t)(n >> 6) * 128 + (n & 63) : (size_t)n;
+      wr[0][f] = wg + gate_row * k_dim;
+      if (GATED) wr[Z - 1][f] = wg + ((GATED && interleaved) ? gate_row + 64 : (size_t)n_out + n) * k_dim;
+    }
+    float acc[Z][F][FEW_ROWS];
 #pragma unroll
-      for (int r = 0; r < FEW_ROWS; ++r) acc[z][r] = 0.f;
+    for (int z = 0; z < Z; ++z)
+#pragma unroll
+      for (int f = 0; f < F; ++f)
+#pragma unroll
+        for (int r = 0; r < FEW_ROWS; ++r) acc[z][f][r] = 0.f;
     for (int k = lane * N; k < k_dim; k += 32 * N) {
-      float w0[N], w1[N];
-      Piece<T>::load(wr0 + k, w0);
-      if (GATED) Piece<T>::load(wr1 + k, w1);
+      float wv[Z][F][N];
+#pragma unroll
+      for (int z = 0; z < Z; ++z)
+#pragma unroll
+        for (int f = 0; f < F; ++f) Piece<T>::load(wr[z][f] + k, wv[z][f]);
 #pragma unroll
       for (int r = 0; r < FEW_ROWS; ++r) {
         if (r < rows) {
           float x[N];
           Piece<T>::load(a + row_of[r] * a_stride + k, x);
 #pragma unroll
-          for (int i = 0; i < N; ++i) {
-            acc[0][r] = fmaf(x[i], w0[i], acc[0][r]);
-            if (GATED) acc[1][r] = fmaf(x[i], w1[i], acc[1][r]);
-          }
+          for (int z = 0; z < Z; ++z)
+#pragma unroll
+            for (int f = 0; f < F; ++f)
+#pragma unroll
+              for (int i = 0; i < N; ++i) acc[z][f][r] = fmaf(x[i], wv[z][f][i], acc[z][f][r]);
         }
       }
     }
 #pragma unroll
-    for (int r = 0; r < FEW_ROWS; ++r) {
-      if (r < rows) {            // uniform over the block
-        const float g = warp_sum(acc[0][r]);
-        const float u = GATED ? warp_sum(acc[GATED ? 1 : 0][r]) : 0.f;
-        if (lane == 0) {
-          const int place = first + r;
-          const long dst = out_rows ? out_rows[place] : place;
-          if (GATED) {
-            const float sc = pair_scale ? pair_scale[order[place]] : 1.f;
-            Elem<OutT>::store(out + dst * out_stride + n, expert_activation<ACT>(sc * g) * (sc * u));
-          } else {
-            Elem<OutT>::store(out + dst * out_stride + n, g);
+    for (int f = 0; f < F; ++f) {
+#pragma unroll
+      for (int r = 0; r < FEW_ROWS; ++r) {
+        if (r < rows) {            // uniform over the block
+          const float g = warp_sum(acc[0][f][r]);
+          const float u = GATED ? warp_sum(acc[Z - 1][f][r]) : 0.f;
+          if (lane == 0 && n0 + f < n_out) {
+            const int place = first + r;
+            const long dst = out_rows ? out_rows[place] : place;
+            if (GATED) {
+              const float sc = pair_scale ? pair_scale[order[place]] : 1.f;
+              Elem<OutT>::store(out + dst * out_stride + n0 + f, expert_activation<ACT>(sc * g) * (sc * u));
+            } else {
+              Elem<OutT>::store(out + dst * out_stride + n0 + f, g);
+            }
           }
         }
       }
@@ -427,8 +446,8 @@ int launch_product(bool few, int act, const void* a, long a_stride, const int* a
     // enough blocks to fill the GPU: the tiles are about the experts in use, the features are dealt over grid y
     int tiles = (n_pairs + FEW_ROWS - 1) / FEW_ROWS + experts;
     if (tiles > n_pairs) tiles = n_pairs;
-    int per_warp = 4;
-    while (per_warp > 1 && (long)tiles * ((n_out + FEW_WARPS * per_warp - 1) / (FEW_WARPS * per_warp)) < 4 * 148) per_warp >>= 1;
+    int per_warp = 8;
+    while (per_warp > FEW_FEATURES && (long)tiles * ((n_out + FEW_WARPS * per_warp - 1) / (FEW_WARPS * per_warp)) < 4 * 148) per_warp >>= 1;
     dim3 grid(tiles, (n_out + FEW_WARPS * per_warp - 1) / (FEW_WARPS * per_warp));
     if (act == 1) lb_launch(moe_expert_rows_kernel<T, OutT, GATED, 1>, grid, FEW_WARPS * 32, 0, stream, LB_MOE_ARGS, per_warp);
     else lb_launch(moe_expert_rows_kernel<T, OutT, GATED, 0>, grid, FEW_WARPS * 32, 0, stream, LB_MOE_ARGS, per_warp);
@@ -454,18 +473,22 @@ int launch_product(bool few, int act, const void* a, long a_stride, const int* a
 template <typename T>
 static void launch_route(const void* h, const float* router, const float* shared_w, int* ids, float* scores,
                          float* shared_factor, int tokens, int hidden, int experts, int top, cudaStream_t stream) {
-  const bool vec = hidden % 4 == 0 && (uintptr_t)router % 16 == 0 && (uintptr_t)shared_w % 16 == 0;
-  // few tokens: a block each, so that the step's latency is one token's; many: eight a block share every weight they read
+  const bool vec = hidden % Piece<T>::N == 0 && (uintptr_t)router % 16 == 0 && (uintptr_t)shared_w % 16 == 0 &&
+                   (uintptr_t)h % 16 == 0;
+#define LB_ROUTE_ARGS (const T*)h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top
+  // few tokens: a block of 32 warps each (a warp an expert or two), so that the step's latency is about one dot product's;
+  // many: eight a block share every weight they read
   if (tokens <= 64) {
     const size_t smem = (size_t)experts * sizeof(float);
-    if (vec) lb_launch(moe_route_kernel<T, 1, true>, tokens, ROUTE_WARPS * 32, smem, stream, (const T*)h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top);
-    else lb_launch(moe_route_kernel<T, 1, false>, tokens, ROUTE_WARPS * 32, smem, stream, (const T*)h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top);
+    if (vec) lb_launch(moe_route_kernel<T, 1, 32, true>, tokens, 1024, smem, stream, LB_ROUTE_ARGS);
+    else lb_launch(moe_route_kernel<T, 1, 32, false>, tokens, 1024, smem, stream, LB_ROUTE_ARGS);
   } else {
     const size_t smem = (size_t)8 * experts * sizeof(float);
     const int blocks = (tokens + 7) / 8;
-    if (vec) lb_launch(moe_route_kernel<T, 8, true>, blocks, ROUTE_WARPS * 32, smem, stream, (const T*)h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top);
-    else lb_launch(moe_route_kernel<T, 8, false>, blocks, ROUTE_WARPS * 32, smem, stream, (const T*)h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top);
+    if (vec) lb_launch(moe_route_kernel<T, 8, 8, true>, blocks, 256, smem, stream, LB_ROUTE_ARGS);
+    else lb_launch(moe_route_kernel<T, 8, 8, false>, blocks, 256, smem, stream, LB_ROUTE_ARGS);
   }
+#undef LB_ROUTE_ARGS
 }
 
 LB_EXPORT int lb_moe_route(int dtype, const void* h, const float* router, const float* shared_w, int* ids, float* scores,

@@ -503,14 +503,15 @@ def moe_group_tiles(ids: torch.Tensor, experts: int, place_of: torch.Tensor, til
                     rows_up: int, rows_down: int) -> None:
     """The grouping for the tensor-core products: place_of[pair] = the pair's row in buffers of `moe_padded_rows` rows where
     every tile of 128 rows belongs to one expert; tile_up[i] / tile_down[i] = expert * rows_up / expert * rows_down for tile
-    i (the row where that expert's weights begin in the stacked matrices), -1 for a tile without pairs."""
+    i (the row where that expert's weights begin in the stacked matrices), -1 for a tile without pairs; the lists have one
+    more entry than the buffers have tiles, the number of tiles in use (all at the front)."""
     for name, t in (("ids", ids), ("place_of", place_of), ("tile_up", tile_up), ("tile_down", tile_down)):
         _need(t, torch.int32, name)
     if place_of.numel() != ids.numel() or tile_up.numel() != tile_down.numel() \
-            or tile_up.numel() * MOE_TILE_ROWS < moe_padded_rows(ids.numel(), experts):
-        raise ValueError("moe_group_tiles: place_of one entry per pair, the tile lists one per tile of the padded buffers")
+            or (tile_up.numel() - 1) * MOE_TILE_ROWS < moe_padded_rows(ids.numel(), experts):
+        raise ValueError("moe_group_tiles: place_of one entry per pair, the tile lists one per tile of the padded buffers and one more")
     fn = _fn("moe", "lb_moe_group_tiles", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(fn(_ptr(ids), ids.numel(), int(experts), _ptr(place_of), _ptr(tile_up), _ptr(tile_down), tile_up.numel(), int(rows_up),
+    _check(fn(_ptr(ids), ids.numel(), int(experts), _ptr(place_of), _ptr(tile_up), _ptr(tile_down), tile_up.numel() - 1, int(rows_up),
               int(rows_down), _stream()), "moe_group_tiles")
 
 
@@ -531,8 +532,8 @@ def moe_scatter_rows(h: torch.Tensor, place_of: torch.Tensor, scale: torch.Tenso
 def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_rows: torch.Tensor, groups: int,
                          epilogue: str | None = None) -> torch.Tensor:
     """out[M, N] = a[M, K] @ w_g[N, K]^T tile by tile: every tile of 128 rows of `a` is multiplied by the weights of ONE
-    group, the [N, K] matrix that begins at row tile_rows[tile] of w [groups * N, K]; tiles whose entry is negative are
-    skipped. tile_rows is int32 on the device, written by an earlier kernel. M is a multiple of 128. epilogue "swiglu" as in
+    group, the [N, K] matrix that begins at row tile_rows[tile] of w [groups * N, K]; tile_rows [M / 128 + 1] ends with the
+    number of tiles in use (all at the front; the others are skipped). It is int32 on the device, written by an earlier kernel. M is a multiple of 128. epilogue "swiglu" as in
     `gemm_tcgen05` (each group's rows interleaved by `interleave_gate_up`)."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != 2:
         raise ValueError("gemm_tcgen05_grouped: operands must be 2-D bfloat16")
@@ -546,8 +547,8 @@ def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ti
     if epilogue == "swiglu" and (n % (2 * SWIGLU_BLOCK) or out.dtype != torch.bfloat16):
         raise ValueError("gemm_tcgen05_grouped: the swiglu epilogue needs interleaved weights and a bfloat16 output")
     _need(tile_rows, torch.int32, "tile_rows")
-    if tuple(out.shape) != (m, out_cols) or out.stride(1) != 1 or tile_rows.numel() < m // MOE_TILE_ROWS:
-        raise ValueError("gemm_tcgen05_grouped: out [M, N] and one tile entry per 128 rows")
+    if tuple(out.shape) != (m, out_cols) or out.stride(1) != 1 or tile_rows.numel() != m // MOE_TILE_ROWS + 1:
+        raise ValueError("gemm_tcgen05_grouped: out [M, N], one tile entry per 128 rows and the count of tiles in use behind them")
     partials, counters, sms = gemm_scratch(a.device)
     fn = _fn("gemm_tcgen05", "lb_gemm_tcgen05_grouped",
              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_long, c_long, c_long, c_void_p, c_void_p, c_long,

@@ -194,15 +194,16 @@ class RoutedExperts(Part):
         ops.moe_route(h, self.router, self.top, ids, scores, self.shared_gate, factor)
         return ids, scores, factor
 
-    GROUPED_FROM = 512      # pairs from which the grouped tensor-core products run (below: the FFMA kernels)
+    FEW_PER_EXPERT = 4      # up to this many pairs per expert on average the weight-streaming kernels run; beyond, in
+                            # bfloat16, the grouped tensor-core products (in float32 the tiled FFMA kernel)
 
     def _forward_grouped(self, h, ids, scores, factor):
         tokens, pairs = h.shape[0], h.shape[0] * self.top
         rows = ops.moe_padded_rows(pairs, self.experts)
         tiles = rows // ops.MOE_TILE_ROWS
         place_of = torch.empty((pairs,), dtype=torch.int32, device=h.device)
-        tile_up = torch.empty((tiles,), dtype=torch.int32, device=h.device)
-        tile_down = torch.empty((tiles,), dtype=torch.int32, device=h.device)
+        tile_up = torch.empty((tiles + 1,), dtype=torch.int32, device=h.device)      # the last entry: the tiles in use
+        tile_down = torch.empty((tiles + 1,), dtype=torch.int32, device=h.device)
         ops.moe_group_tiles(ids, self.experts, place_of, tile_up, tile_down, 2 * self.inter, self.hidden)
         scaled = torch.empty((rows, self.hidden), dtype=h.dtype, device=h.device)
         ops.moe_scatter_rows(h, place_of, scores, scaled, self.top)
@@ -223,7 +224,7 @@ class RoutedExperts(Part):
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         tokens, pairs = h.shape[0], h.shape[0] * self.top
         ids, scores, factor = self.route(h)
-        if self.grouped and pairs >= self.GROUPED_FROM:
+        if self.grouped and pairs > self.FEW_PER_EXPERT * self.experts:
             return self._forward_grouped(h, ids, scores, factor)
         offsets = torch.empty((self.experts + 1,), dtype=torch.int32, device=h.device)
         order = torch.empty((pairs,), dtype=torch.int32, device=h.device)
