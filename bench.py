@@ -949,6 +949,15 @@ def limazen_kernels(pk: dict) -> dict:
         factor = torch.empty(tokens, device=dev)
         point(f"moe_route_{tokens}", lambda i: ops.moe_route(h[i % ROT], router, top, ids, scores, sgw, factor), ROT,
               nbytes=tokens * width * 2 + (experts + 1) * width * 4)
+        if tokens > 64:      # as a bfloat16 run routes many tokens: the run's product with 32-bit output, then the selection
+            stacked = torch.zeros(-(-(experts + 1) // 8) * 8, width, device=dev, dtype=bf)
+            stacked[:experts], stacked[experts] = router.to(bf), sgw.to(bf)
+            logits = torch.empty(tokens, stacked.shape[0], device=dev)
+
+            def route_product(i):
+                ops.gemm_tcgen05(h[i % ROT], stacked, logits)
+                ops.moe_select(logits, experts, top, ids, scores, factor)
+            point(f"moe_route_product_{tokens}", route_product, ROT, nbytes=tokens * width * 2 + (experts + 1) * width * 2)
         pairs = tokens * top
         gate_up = [torch.randn(experts * 2 * expert_ff, width, device=dev, dtype=bf) * 0.02 for _ in range(2)]
         down = [torch.randn(experts * width, expert_ff, device=dev, dtype=bf) * 0.02 for _ in range(2)]

@@ -769,12 +769,14 @@ LB_EXPORT int lb_qk_rownorm_kv(int dtype, const void* proj, long row_stride, voi
 // in 32-bit, rounded once at the store of out. The variance is the mean of the squared deviations
 // from the mean (two passes over the row, which sits in shared memory). One block per row; the
 // block size depends on the width only, so a row's sums do not depend on the batch.
-template <typename T>
+// VEC: the width is a multiple of 4 and every row starts on a 16-byte (8-byte for bf16) boundary: four elements an
+// access. Which form runs depends on the width and the buffers' alignment only, never on the batch.
+template <typename T, bool VEC>
 __global__ void residual_layernorm_kernel(float* __restrict__ x, const T* __restrict__ delta_a,
                                           const T* __restrict__ delta_b, const float* __restrict__ weight,
                                           const float* __restrict__ bias, T* __restrict__ out,
                                           const int* __restrict__ rows, int hidden, float eps) {
-  extern __shared__ float row_vals[];  // hidden floats + 33 for the reductions
+  extern __shared__ __align__(16) float row_vals[];  // hidden floats + 33 for the reductions
   pdl_launch_dependents();
   pdl_wait();
   float* scratch = row_vals + hidden;
@@ -783,26 +785,81 @@ __global__ void residual_layernorm_kernel(float* __restrict__ x, const T* __rest
   const T* ar = delta_a ? delta_a + src * hidden : nullptr;
   const T* br = delta_b ? delta_b + src * hidden : nullptr;
   float sum = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = xr[i];
-    if (ar && br) v += Elem<T>::load(ar + i) + Elem<T>::load(br + i);   // the sub-layers' sum joins the stream
-    else if (ar) v += Elem<T>::load(ar + i);
-    else if (br) v += Elem<T>::load(br + i);
-    if (!rows && (ar || br)) xr[i] = v;
-    row_vals[i] = v;
-    sum += v;
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      float4 v = Four<float>::load(xr + i);
+      if (ar && br) {                                  // the sub-layers' sum joins the stream
+        const float4 a = Four<T>::load(ar + i), b = Four<T>::load(br + i);
+        v.x += a.x + b.x; v.y += a.y + b.y; v.z += a.z + b.z; v.w += a.w + b.w;
+      } else if (ar || br) {
+        const float4 a = Four<T>::load((ar ? ar : br) + i);
+        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+      }
+      if (!rows && (ar || br)) Four<float>::store(xr + i, v);
+      Four<float>::store(row_vals + i, v);
+      sum += (v.x + v.y) + (v.z + v.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = xr[i];
+      if (ar && br) v += Elem<T>::load(ar + i) + Elem<T>::load(br + i);
+      else if (ar) v += Elem<T>::load(ar + i);
+      else if (br) v += Elem<T>::load(br + i);
+      if (!rows && (ar || br)) xr[i] = v;
+      row_vals[i] = v;
+      sum += v;
+    }
   }
   if (!weight) return;
   const float mean = block_sum(sum, scratch) / (float)hidden;
   float sq = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float d = row_vals[i] - mean;
-    sq += d * d;
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      const float4 v = Four<float>::load(row_vals + i);
+      const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+      sq += (a * a + b * b) + (c * c + d * d);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float d = row_vals[i] - mean;
+      sq += d * d;
+    }
   }
   const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)hidden + eps);
   T* o = out + (size_t)blockIdx.x * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-    Elem<T>::store(o + i, (row_vals[i] - mean) * inv * weight[i] + (bias ? bias[i] : 0.f));
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      const float4 v = Four<float>::load(row_vals + i), w = Four<float>::load(weight + i);
+      const float4 b = bias ? Four<float>::load(bias + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      Four<T>::store(o + i, make_float4((v.x - mean) * inv * w.x + b.x, (v.y - mean) * inv * w.y + b.y,
+                                        (v.z - mean) * inv * w.z + b.z, (v.w - mean) * inv * w.w + b.w));
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+      Elem<T>::store(o + i, (row_vals[i] - mean) * inv * weight[i] + (bias ? bias[i] : 0.f));
+  }
+}
+
+template <typename T>
+static int launch_residual_layernorm(float* x, const void* delta_a, const void* delta_b, const float* weight, const float* bias,
+                                     void* out, const int* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
+  static LbPerDeviceOnce once;
+  const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+  if (smem > 200 * 1024) return LB_ERR_SIZE;
+  if (smem > 48 * 1024 && once.first()) {
+    cudaFuncSetAttribute(residual_layernorm_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(residual_layernorm_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  }
+  const bool vec = hidden % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)delta_a % 16 == 0 && (uintptr_t)delta_b % 16 == 0 &&
+                   (uintptr_t)out % 16 == 0 && (uintptr_t)weight % 16 == 0 && (uintptr_t)bias % 16 == 0;
+  const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+  if (vec)
+    lb_launch(residual_layernorm_kernel<T, true>, n_rows, threads, smem, stream, x, (const T*)delta_a, (const T*)delta_b, weight,
+              bias, (T*)out, rows, hidden, eps);
+  else
+    lb_launch(residual_layernorm_kernel<T, false>, n_rows, threads, smem, stream, x, (const T*)delta_a, (const T*)delta_b, weight,
+              bias, (T*)out, rows, hidden, eps);
+  return lb_last_error();
 }
 
 LB_EXPORT int lb_residual_layernorm(int dtype, float* x, const void* delta_a, const void* delta_b, const float* weight,
@@ -810,23 +867,11 @@ LB_EXPORT int lb_residual_layernorm(int dtype, float* x, const void* delta_a, co
                                     cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (hidden <= 0 || (weight && !out)) return LB_ERR_SIZE;
-  static LbPerDeviceOnce once;
-  const size_t smem = (size_t)(hidden + 33) * sizeof(float);
-  if (smem > 200 * 1024) return LB_ERR_SIZE;
-  if (smem > 48 * 1024 && once.first()) {
-    cudaFuncSetAttribute(residual_layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    cudaFuncSetAttribute(residual_layernorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-  }
-  const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
   if (dtype == LB_F32)
-    lb_launch(residual_layernorm_kernel<float>, n_rows, threads, smem, stream, x, (const float*)delta_a,
-              (const float*)delta_b, weight, bias, (float*)out, rows, hidden, eps);
-  else if (dtype == LB_BF16)
-    lb_launch(residual_layernorm_kernel<bf16>, n_rows, threads, smem, stream, x, (const bf16*)delta_a, (const bf16*)delta_b,
-              weight, bias, (bf16*)out, rows, hidden, eps);
-  else
-    return LB_ERR_DTYPE;
-  return lb_last_error();
+    return launch_residual_layernorm<float>(x, delta_a, delta_b, weight, bias, out, rows, n_rows, hidden, eps, stream);
+  if (dtype == LB_BF16)
+    return launch_residual_layernorm<bf16>(x, delta_a, delta_b, weight, bias, out, rows, n_rows, hidden, eps, stream);
+  return LB_ERR_DTYPE;
 }
 
 // ---------------------------------------------------------------- biases + partial rotation + value blend + KV write

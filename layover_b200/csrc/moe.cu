@@ -133,6 +133,47 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
   }
 }
 
+// The same choice from logits that a matrix product left in memory (a bfloat16 run: products of bfloat16 numbers are
+// exact in 32-bit and the tensor cores add them up in 32-bit, so these are 32-bit logits): row t of `logits` holds the
+// experts' logits and, behind them, the shared expert's. A warp per token.
+constexpr int SELECT_WARPS = 4;
+__global__ void __launch_bounds__(SELECT_WARPS * 32)
+moe_select_kernel(const float* __restrict__ logits, long stride, int* __restrict__ ids, float* __restrict__ scores,
+                  float* __restrict__ shared_factor, int tokens, int experts, int top) {
+  extern __shared__ float picked[];                 // [SELECT_WARPS][experts]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * SELECT_WARPS + warp;
+  if (t >= tokens) return;
+  float* z = picked + warp * experts;
+  const float* row = logits + (size_t)t * stride;
+  for (int e = lane; e < experts; e += 32) z[e] = row[e];
+  if (shared_factor && lane == 0) shared_factor[t] = 1.0f / (1.0f + expf(-row[experts]));
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = z[e];
+      if (v > best || (v == best && e < at)) { best = v; at = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at >= experts) at = k;                      // only when every logit left is NaN or -inf
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = at;
+      scores[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
+      z[at] = -INFINITY;                            // taken
+    }
+    __syncwarp();
+  }
+}
+
 // One block: count, scan, place. The order inside a group is the order of arrival; no result depends on it.
 __global__ void __launch_bounds__(1024)
 moe_group_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ offsets, int* __restrict__ order) {
@@ -499,6 +540,17 @@ LB_EXPORT int lb_moe_route(int dtype, const void* h, const float* router, const 
   if (dtype == LB_F32) launch_route<float>(h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top, stream);
   else if (dtype == LB_BF16) launch_route<bf16>(h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top, stream);
   else return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
+// ids, scores (and shared_factor, from column `experts`, when not null) from logits [tokens, >= experts (+ 1)] with row
+// stride `stride` floats.
+LB_EXPORT int lb_moe_select(const float* logits, long stride, int* ids, float* scores, float* shared_factor, int tokens,
+                            int experts, int top, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (experts <= 0 || top <= 0 || top > experts || experts > 1024 || stride < experts + (shared_factor ? 1 : 0)) return LB_ERR_SIZE;
+  lb_launch(moe_select_kernel, (tokens + SELECT_WARPS - 1) / SELECT_WARPS, SELECT_WARPS * 32,
+            (size_t)SELECT_WARPS * experts * sizeof(float), stream, logits, stride, ids, scores, shared_factor, tokens, experts, top);
   return lb_last_error();
 }
 

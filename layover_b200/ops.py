@@ -422,6 +422,23 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor
               hidden, experts, int(top), _stream()), "moe_route")
 
 
+def moe_select(logits: torch.Tensor, experts: int, top: int, ids: torch.Tensor, scores: torch.Tensor,
+               shared_factor: torch.Tensor | None = None) -> None:
+    """What `moe_route` chooses, from router logits that a matrix product left in float32 [T, >= experts (+ 1)]: the
+    `top` largest of the first `experts` columns (ties: the lower index), their sigmoids, and, with `shared_factor`,
+    sigmoid of column `experts`."""
+    _need(ids, torch.int32, "ids"); _need(scores, torch.float32, "scores")
+    tokens = logits.shape[0]
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1 or tuple(ids.shape) != (tokens, top) \
+            or tuple(scores.shape) != (tokens, top) or logits.shape[1] < experts + (1 if shared_factor is not None else 0):
+        raise ValueError("moe_select: shapes do not agree")
+    if shared_factor is not None:
+        _need(shared_factor, torch.float32, "shared_factor")
+    fn = _fn("moe", "lb_moe_select", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(logits), logits.stride(0), _ptr(ids), _ptr(scores), _ptr(shared_factor), tokens, int(experts), int(top),
+              _stream()), "moe_select")
+
+
 def moe_group(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor) -> None:
     """Group the (token, k) pairs by expert: order int32 [pairs] lists the pairs expert by expert, expert e's at places
     offsets[e] .. offsets[e + 1] (offsets int32 [experts + 1])."""

@@ -122,6 +122,10 @@ class RoutedExperts(Part):
     token's experts with the shared expert in the same kernel. Nothing comes back to the host in between,
     so a step with routed layers is captured in a CUDA graph like any other.
 
+    The router is a kernel of its own (a warp's 32-bit dot product per logit); for many tokens in a bfloat16 run
+    whose router weights are bfloat16 numbers it is the run's tensor-core product with 32-bit output, which is the
+    same arithmetic, followed by the selection kernel.
+
     Two forms of the products. Few pairs (decode steps), and every float32 run: FFMA kernels that gather the
     rows by index, take the score into the 32-bit sums and stream each chosen expert's weights once. Many
     pairs in a bfloat16 run: the pairs' rows, scaled by their scores, are laid out expert by expert in tiles
@@ -181,6 +185,16 @@ class RoutedExperts(Part):
         if self.shared is not None:
             self.shared.bind(tensors, runtime)
         self.shared_gate = tensors[self.shared_gate_name].reshape(-1).contiguous() if self.shared_gate_name else None
+        # In a bfloat16 run whose router weights are bfloat16 numbers, the logits of many tokens are one tensor-core
+        # product: bfloat16 x bfloat16 is exact in 32-bit and the sums are 32-bit, so these are 32-bit logits.
+        self.router_matrix = None
+        if runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0:
+            rows = [self.router] + ([self.shared_gate[None]] if self.shared_gate is not None else [])
+            stacked = torch.cat(rows, dim=0)
+            if bool((stacked.to(torch.bfloat16).float() == stacked).all()):
+                padded = torch.zeros((-(-stacked.shape[0] // 8) * 8, self.hidden), dtype=torch.bfloat16, device=stacked.device)
+                padded[: stacked.shape[0]] = stacked.to(torch.bfloat16)
+                self.router_matrix = padded
 
     def kernel_libraries(self, dtype):
         return ("elementwise", "moe") + (("gemm_tcgen05",) if dtype == torch.bfloat16 else ())
@@ -191,9 +205,14 @@ class RoutedExperts(Part):
         ids = torch.empty((tokens, self.top), dtype=torch.int32, device=h.device)
         scores = torch.empty((tokens, self.top), dtype=torch.float32, device=h.device)
         factor = torch.empty((tokens,), dtype=torch.float32, device=h.device) if self.shared_gate is not None else None
-        ops.moe_route(h, self.router, self.top, ids, scores, self.shared_gate, factor)
+        if self.router_matrix is not None and tokens > self.ROUTE_PRODUCT_FROM:
+            logits = self.runtime.linear(h, self.router_matrix, out_dtype=torch.float32)
+            ops.moe_select(logits, self.experts, self.top, ids, scores, factor)
+        else:
+            ops.moe_route(h, self.router, self.top, ids, scores, self.shared_gate, factor)
         return ids, scores, factor
 
+    ROUTE_PRODUCT_FROM = 64 # tokens beyond which a bfloat16 run's router logits are a tensor-core product
     FEW_PER_EXPERT = 4      # up to this many pairs per expert on average the weight-streaming kernels run; beyond, in
                             # bfloat16, the grouped tensor-core products (in float32 the tiled FFMA kernel)
 
