@@ -28,15 +28,17 @@ namespace {
 template <typename T> struct Piece;
 template <> struct Piece<float> {
   static constexpr int N = 4;
-  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
-    const float4 r = *reinterpret_cast<const float4*>(p);
-    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  static __device__ __forceinline__ uint4 raw(const float* p) { return *reinterpret_cast<const uint4*>(p); }
+  static __device__ __forceinline__ void unpack(const uint4& r, float (&v)[4]) {
+    v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y); v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
   }
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) { unpack(raw(p), v); }
 };
 template <> struct Piece<bf16> {
   static constexpr int N = 8;
-  static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
-    const uint4 r = *reinterpret_cast<const uint4*>(p);
+  static __device__ __forceinline__ uint4 raw(const bf16* p) { return *reinterpret_cast<const uint4*>(p); }
+  static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) { unpack(raw(p), v); }
+  static __device__ __forceinline__ void unpack(const uint4& r, float (&v)[8]) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -244,6 +246,30 @@ __global__ void moe_scatter_rows_kernel(const T* __restrict__ h, long h_stride, 
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) Elem<T>::store(dst + i, s * Elem<T>::load(src + i));
 }
 
+// Which expert's rows block `tile` of a products' launch owns, when every expert's group is cut into tiles of `rows_per_tile`
+// places: all threads read the group sizes at once (one round trip to memory), thread 0 walks the tiles' counts in shared
+// memory. found[0] = expert (-1: no such tile), found[1] = first place, found[2] = places. `counts`: `experts` ints.
+__device__ __forceinline__ void find_tile(const int* __restrict__ offsets, int experts, int rows_per_tile, int tile,
+                                          int* counts, int* found) {
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = offsets[e + 1] - offsets[e];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int left = tile, expert = -1, first = 0, rows = 0, begin = 0;
+    for (int e = 0; e < experts && expert < 0; ++e) {
+      const int count = counts[e], tiles = (count + rows_per_tile - 1) / rows_per_tile;
+      if (left < tiles) {
+        expert = e;
+        first = begin + left * rows_per_tile;
+        rows = min(rows_per_tile, count - left * rows_per_tile);
+      }
+      left -= tiles;
+      begin += count;
+    }
+    found[0] = expert; found[1] = first; found[2] = rows;
+  }
+  __syncthreads();
+}
+
 template <int ACT> __device__ __forceinline__ float expert_activation(float g) {
   if (ACT == 1) return fmaxf(g, 0.f);
   return g / (1.0f + expf(-g));      // silu
@@ -266,24 +292,12 @@ moe_expert_product_kernel(const T* __restrict__ a, long a_stride, const int* __r
   constexpr int BK = 32, THREADS = (BM / TM) * (BN / TN);
   __shared__ float a_s[BK][BM + 1];
   __shared__ float w_s[GATED ? 2 : 1][BK][BN + 1];
-  __shared__ int tile_expert, tile_first, tile_rows;
+  __shared__ int found[3];
+  extern __shared__ int group_counts[];          // [experts]
   pdl_launch_dependents();
   pdl_wait();
-  if (threadIdx.x == 0) {
-    int left = blockIdx.x, found = -1, first = 0, rows = 0;
-    for (int e = 0; e < experts && found < 0; ++e) {
-      const int begin = offsets[e], count = offsets[e + 1] - begin, tiles = (count + BM - 1) / BM;
-      if (left < tiles) {
-        found = e;
-        first = begin + left * BM;
-        rows = min(BM, count - left * BM);
-      }
-      left -= tiles;
-    }
-    tile_expert = found; tile_first = first; tile_rows = rows;
-  }
-  __syncthreads();
-  const int expert = tile_expert, first = tile_first, rows = tile_rows;
+  find_tile(offsets, experts, BM, blockIdx.x, group_counts, found);
+  const int expert = found[0], first = found[1], rows = found[2];
   if (expert < 0) return;
   const int n0 = blockIdx.y * BN;
   const T* wg = w + (size_t)expert * expert_stride;
@@ -371,27 +385,16 @@ moe_expert_rows_kernel(const T* __restrict__ a, long a_stride, const int* __rest
                        const int* __restrict__ out_rows, const float* __restrict__ pair_scale,
                        const int* __restrict__ order, int interleaved, int features_per_warp) {
   constexpr int N = Piece<T>::N, Z = GATED ? 2 : 1, F = FEW_FEATURES;
-  __shared__ int tile_expert, tile_first, tile_rows;
+  __shared__ int found[3];
   __shared__ long row_of[FEW_ROWS];
+  extern __shared__ int group_counts[];          // [experts]
   pdl_launch_dependents();
   pdl_wait();
-  if (threadIdx.x == 0) {
-    int left = blockIdx.x, found = -1, first = 0, rows = 0;
-    for (int e = 0; e < experts && found < 0; ++e) {
-      const int begin = offsets[e], count = offsets[e + 1] - begin, tiles = (count + FEW_ROWS - 1) / FEW_ROWS;
-      if (left < tiles) {
-        found = e;
-        first = begin + left * FEW_ROWS;
-        rows = min(FEW_ROWS, count - left * FEW_ROWS);
-      }
-      left -= tiles;
-    }
-    tile_expert = found; tile_first = first; tile_rows = rows;
-    for (int r = 0; r < rows; ++r) row_of[r] = a_rows ? a_rows[first + r] / a_div : first + r;
-  }
-  __syncthreads();
-  const int expert = tile_expert, first = tile_first, rows = tile_rows;
+  find_tile(offsets, experts, FEW_ROWS, blockIdx.x, group_counts, found);
+  const int expert = found[0], first = found[1], rows = found[2];
   if (expert < 0) return;
+  if (threadIdx.x < rows) row_of[threadIdx.x] = a_rows ? a_rows[first + threadIdx.x] / a_div : first + threadIdx.x;
+  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* wg = w + (size_t)expert * expert_stride;
   const int f0 = (blockIdx.y * FEW_WARPS + warp) * features_per_warp;
@@ -412,12 +415,26 @@ moe_expert_rows_kernel(const T* __restrict__ a, long a_stride, const int* __rest
       for (int f = 0; f < F; ++f)
 #pragma unroll
         for (int r = 0; r < FEW_ROWS; ++r) acc[z][f][r] = 0.f;
+    // the next 16 bytes of every weight row are asked for (and kept as they come) before this step's are used
+    uint4 ahead[Z][F];
+    if (lane * N < k_dim) {
+#pragma unroll
+      for (int z = 0; z < Z; ++z)
+#pragma unroll
+        for (int f = 0; f < F; ++f) ahead[z][f] = Piece<T>::raw(wr[z][f] + lane * N);
+    }
     for (int k = lane * N; k < k_dim; k += 32 * N) {
       float wv[Z][F][N];
 #pragma unroll
       for (int z = 0; z < Z; ++z)
 #pragma unroll
-        for (int f = 0; f < F; ++f) Piece<T>::load(wr[z][f] + k, wv[z][f]);
+        for (int f = 0; f < F; ++f) Piece<T>::unpack(ahead[z][f], wv[z][f]);
+      if (k + 32 * N < k_dim) {
+#pragma unroll
+        for (int z = 0; z < Z; ++z)
+#pragma unroll
+          for (int f = 0; f < F; ++f) ahead[z][f] = Piece<T>::raw(wr[z][f] + k + 32 * N);
+      }
 #pragma unroll
       for (int r = 0; r < FEW_ROWS; ++r) {
         if (r < rows) {
@@ -490,20 +507,20 @@ int launch_product(bool few, int act, const void* a, long a_stride, const int* a
     int per_warp = 8;
     while (per_warp > FEW_FEATURES && (long)tiles * ((n_out + FEW_WARPS * per_warp - 1) / (FEW_WARPS * per_warp)) < 4 * 148) per_warp >>= 1;
     dim3 grid(tiles, (n_out + FEW_WARPS * per_warp - 1) / (FEW_WARPS * per_warp));
-    if (act == 1) lb_launch(moe_expert_rows_kernel<T, OutT, GATED, 1>, grid, FEW_WARPS * 32, 0, stream, LB_MOE_ARGS, per_warp);
-    else lb_launch(moe_expert_rows_kernel<T, OutT, GATED, 0>, grid, FEW_WARPS * 32, 0, stream, LB_MOE_ARGS, per_warp);
+    if (act == 1) lb_launch(moe_expert_rows_kernel<T, OutT, GATED, 1>, grid, FEW_WARPS * 32, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS, per_warp);
+    else lb_launch(moe_expert_rows_kernel<T, OutT, GATED, 0>, grid, FEW_WARPS * 32, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS, per_warp);
   } else if (few) {      // the same through tiles of 8 places, for sizes and addresses that cannot be read 16 bytes at a time
     constexpr int BM = 8, BN = 128;
     dim3 grid((n_pairs + BM - 1) / BM + experts, (n_out + BN - 1) / BN);
     if (grid.x > (unsigned)n_pairs) grid.x = n_pairs;   // every tile holds a pair
-    if (act == 1) lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 1, 4, GATED, 1>, grid, 256, 0, stream, LB_MOE_ARGS);
-    else lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 1, 4, GATED, 0>, grid, 256, 0, stream, LB_MOE_ARGS);
+    if (act == 1) lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 1, 4, GATED, 1>, grid, 256, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS);
+    else lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 1, 4, GATED, 0>, grid, 256, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS);
   } else {
     constexpr int BM = 64, BN = 64;
     dim3 grid((n_pairs + BM - 1) / BM + experts, (n_out + BN - 1) / BN);
     if (grid.x > (unsigned)n_pairs) grid.x = n_pairs;
-    if (act == 1) lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 4, 4, GATED, 1>, grid, 256, 0, stream, LB_MOE_ARGS);
-    else lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 4, 4, GATED, 0>, grid, 256, 0, stream, LB_MOE_ARGS);
+    if (act == 1) lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 4, 4, GATED, 1>, grid, 256, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS);
+    else lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 4, 4, GATED, 0>, grid, 256, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS);
   }
 #undef LB_MOE_ARGS
   return lb_last_error();
@@ -568,7 +585,7 @@ LB_EXPORT int lb_moe_expert_up(int dtype, const void* h, long h_stride, const in
                                const float* scores, const void* gate_up, void* act, int n_pairs, int top, int experts,
                                int hidden, int inter, int activation, int interleaved, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
-  if (experts <= 0 || hidden <= 0 || inter <= 0 || top <= 0 || activation < 0 || activation > 1) return LB_ERR_SIZE;
+  if (experts <= 0 || experts > 1024 || hidden <= 0 || inter <= 0 || top <= 0 || activation < 0 || activation > 1) return LB_ERR_SIZE;
   if (interleaved && inter % 64) return LB_ERR_SIZE;
   const bool few = n_pairs <= 4 * experts;
   const long expert_stride = 2L * inter * hidden;
@@ -585,7 +602,7 @@ LB_EXPORT int lb_moe_expert_up(int dtype, const void* h, long h_stride, const in
 LB_EXPORT int lb_moe_expert_down(int dtype, const void* act, const int* order, const int* offsets, const void* down, float* y,
                                  int n_pairs, int experts, int hidden, int inter, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
-  if (experts <= 0 || hidden <= 0 || inter <= 0) return LB_ERR_SIZE;
+  if (experts <= 0 || experts > 1024 || hidden <= 0 || inter <= 0) return LB_ERR_SIZE;
   const bool few = n_pairs <= 4 * experts;
   const long expert_stride = (long)hidden * inter;
   if (dtype == LB_F32)
