@@ -868,10 +868,10 @@ def limazen_pair(size: str):
     from layover_b200.config.limazen import limazen_layer
 
     width, heads, kv, dim, experts, top, expert_ff, shared = LIMAZEN_SIZES[size]
-    layer = limazen_layer(heads, kv, dim, dim, LIMAZEN_CHUNK, rot_dims=dim // 2, base=50000.0, factor=4.0,
+    layer = limazen_layer(heads, kv, dim, dim, LIMAZEN_CHUNK, rot_dims=dim // 2, base=10000.0, factor=2.0,
                           ff=None if experts else shared, experts=experts or None, top=top, expert_ff=expert_ff,
                           shared_ff=shared if experts else None)
-    limazen = lb.LimazenConfig(vocab=LIMAZEN_VOCAB, width=width, layers=(layer,) * LIMAZEN_LAYERS, logit_softcap=30.0)
+    limazen = lb.LimazenConfig(vocab=LIMAZEN_VOCAB, width=width, layers=(layer,) * LIMAZEN_LAYERS, logit_softcap=25.0)
     qwen = lb.Qwen3Config(vocab_size=LIMAZEN_VOCAB, hidden_size=width, intermediate_size=top * expert_ff + shared,
                           num_hidden_layers=LIMAZEN_LAYERS, num_attention_heads=heads, num_key_value_heads=kv, head_dim=dim,
                           max_position_embeddings=40960, tie_word_embeddings=False)

@@ -44,7 +44,7 @@ CONFIGS = {
     # head sizes that are multiples of 16: the tensor-core attention in bfloat16, keys and values of different sizes on
     # pages of the larger size; the first layer does not blend, so the second is the one whose values are kept
     "wide_heads": config(150, 96, [
-        layer(4, 1, 32, 16, 40, 16, 50000.0, 4.0, 0.2, False, moe(6, 3, 16, shared=48)),
+        layer(4, 1, 32, 16, 40, 16, 20000.0, 5.0, 0.2, False, moe(6, 3, 16, shared=48)),
         layer(2, 2, 16, 48, 33, 16, 10000.0, 2.0, 0.3, True, dense(64)),
         layer(6, 2, 64, 48, 7, 32, 10000.0, None, 0.15, True, moe(4, 4, 24, shared=16)),
         layer(4, 2, 48, 48, 64, 48, 1000.0, 8.0, 0.18, True, dense(80)),
