@@ -176,6 +176,30 @@ def test_chunked_attention_sees_exactly_its_chunk(dtype, heads, kv, d, e, chunk)
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES.values()))
+@pytest.mark.parametrize("heads,kv,d,e", [(4, 2, 32, 16), (2, 2, 8, 20)])
+def test_a_key_hundreds_of_tokens_back_in_the_same_chunk_decides(dtype, heads, kv, d, e):
+    """The last query points at key 3 of a 700-token request under a chunk of 1,024 (and, under a chunk of 512, at a
+    key that the chunk's border hides): among hundreds of keys one score stands out, as a prompt, decoded, and cut."""
+    scale, n = 0.3, 700
+    gen = torch.Generator().manual_seed(d)
+    for chunk in (1024, 512):
+        spec, tensors, sizes = identity_attention(heads, kv, d, e, chunk, scale)
+        part, cache, step = mixer_harness(spec, tensors, dtype, page_tokens=16, pages=3 * 48)
+        rows = torch.randn(n, sum(sizes), generator=gen) * 0.5
+        direction = torch.zeros(d)
+        direction[3] = 6.0
+        for h in range(heads):
+            rows[n - 1, h * d:(h + 1) * d] = direction
+        for g in range(kv):
+            rows[3, sizes[0] + g * d: sizes[0] + (g + 1) * d] = direction
+        rows = rows.to(dtype).float()
+        want = plain_identity_attention(rows, sizes, heads, kv, d, e, chunk, scale)
+        for cuts in ([n], [n - 1, 1], [n - 30] + [1] * 30, [300, 2, 398]):
+            close(run_cuts(cache, step, rows, cuts)[:, : heads * e], want, dtype, f"chunk {chunk}, cuts {cuts[:3]}")
+        cache.check()
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES.values()))
 @pytest.mark.parametrize("d,rotated,factor", [(16, 16, 1.0), (16, 8, 4.0), (12, 2, 0.5), (32, 20, 3.0)])
 def test_rotation_turns_the_first_channels_by_the_scaled_position(dtype, d, rotated, factor):
     """Keys far from the query: positions up to 300 under a fast base, so a wrong frequency, a wrong pairing
