@@ -17,6 +17,13 @@
 //             what else is in the batch. (For designs that weight the expert's output the same
 //             kernels serve: up with s = 1, the weight in `combine`.)
 //   combine   out[t] = T(sum_k y[t * top + k] * (c_k) + f_t * shared[t]), c_k = 1 or the pair's score
+//
+// Three forms of the products: `moe_expert_rows_kernel` for a few rows per expert (decode steps: a stream of the chosen
+// experts' weight rows, 16 bytes a load), `moe_expert_product_kernel` in tiles on the FFMA pipes (32-bit runs with many
+// pairs, and sizes that cannot be read 16 bytes at a time), and for many pairs in a bfloat16 run the tensor-core product
+// of gemm_tcgen05.cu in its grouped form, for which `moe_group_tiles_kernel` pads every expert's group to whole tiles of
+// 128 rows and `moe_scatter_rows_kernel` lays the scaled rows out (the score then multiplies the rounded input itself).
+// In a bfloat16 run with many tokens the router's logits may also come from that product (`moe_select_kernel`).
 #include <math.h>
 
 #include "common.cuh"

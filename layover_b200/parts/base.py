@@ -15,8 +15,9 @@ What each kind must offer:
                   kernel_libraries(dtype) -> names    kernel libraries it launches (default: none)
                   tile_sizes(dtype) -> sizes          query-tile lists it wants in a batch (default: none)
   norm            forward(x, delta, rows=None, extra=None) -> h
-                                                      x += delta in place (delta may be None, or a sub-layer's
-                                                      output that is still to be normed: `Deferred`), h = norm(x);
+                                                      x += delta in place (delta may be None, a sub-layer's
+                                                      output that is still to be normed: `Deferred`, or, for a
+                                                      layernorm, a pair of outputs of a parallel block), h = norm(x);
                                                       with rows, only those rows, x untouched; extra: one more
                                                       tensor to add (the embedding output between passes)
   position        tables(batch) -> float32 [T, 2, dim/2] cos/sin of the step, or None; made once per
